@@ -1,0 +1,309 @@
+#!/usr/bin/env python
+"""Benchmark of the LSTM hot path (one JSON line on stdout, printed by rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1..c5] [--impl ours|reference]
+
+A step is one forward+backward pass (forward only for c2) of the stacked LSTM
+over one batch of seeded synthetic input.  Workloads are the BASELINE configs;
+the default (c5: 2-layer bf16, global B=4096 split over the ranks, T=256,
+I=H=512, fwd+bwd, weight-gradient allreduce) is the one whose metric is quoted
+at 1/2/4/8 GPUs, so the same workload runs at every N (strong scaling).
+
+  value     whole-job layer-tokens/s (L*B*T per step / time), inputs resident in HBM
+  e2e       same metric through FastLSTM with pinned-host inputs copied in and the
+            final hidden state copied out inside the timed region
+  roofline  the persistent forward-recurrence kernel timed alone with CUDA events
+  cpu_baseline / --impl reference
+            torch.nn.LSTM fp32 on the host cores (the reference project's own CPU
+            oracle), on a bounded batch sample of the same workload
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: dtype, L, B(global), T, I=H, backward, batch_first, h0_std, terminal grads
+    "c1": dict(dtype="fp32", L=1, B=16, T=64, H=128, bwd=True, batch_first=True, h0=0.1, term=True),
+    "c2": dict(dtype="fp16", L=1, B=64, T=1024, H=256, bwd=False, batch_first=False, h0=0.0, term=False),
+    "c3": dict(dtype="fp16", L=1, B=256, T=512, H=1024, bwd=True, batch_first=False, h0=0.01, term=False),
+    "c4": dict(dtype="bf16", L=1, B=32, T=1024, H=2048, bwd=True, batch_first=False, h0=0.0, term=False),
+    "c5": dict(dtype="bf16", L=2, B=4096, T=256, H=512, bwd=True, batch_first=False, h0=0.0, term=False),
+}
+ESIZE = {"fp32": 4, "fp16": 2, "bf16": 2}
+CPU_SAMPLE_BATCH = {"c1": 16, "c2": 64, "c3": 32, "c4": 32, "c5": 64}
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) every 100 ms."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.mhz, self.reasons, self.max_mhz = index, False, [], set(), None
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+                getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            }
+            while not self.stop_flag:
+                self.mhz.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(0.1)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def result(self):
+        return {"sm_mhz": statistics.median(self.mhz) if self.mhz else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def cpu_baseline(wl, cfg, steps=1, warmup=1):
+    """nn.LSTM fp32 on the host cores over a batch sample of the workload."""
+    from oracle.torch_cpu import time_nn_lstm
+    bs = min(CPU_SAMPLE_BATCH[wl], cfg["B"])
+    times = []
+    threads = os.cpu_count() or 1
+    for i in range(warmup + steps):
+        t, threads = time_nn_lstm(cfg["H"], cfg["H"], cfg["L"], cfg["T"], bs, cfg["bwd"], reps=0,
+                                  seed=1000 + i, threads=threads)
+        if i >= warmup:
+            times.append(t)
+    sec = sum(times) / len(times)
+    return {"value": cfg["L"] * bs * cfg["T"] / sec, "unit": "tokens/s", "cores": threads,
+            "kind": "port",
+            "sample": f"torch.nn.LSTM fp32 CPU, batch sample {bs} of {cfg['B']}, full T={cfg['T']}, "
+                      f"L={cfg['L']}, {'fwd+bwd' if cfg['bwd'] else 'fwd'}; {sec:.3f} s per pass"}, sec
+
+
+def run_reference(args, wl, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    base, sec = cpu_baseline(wl, cfg, steps=max(1, args.steps), warmup=max(1, min(args.warmup, 2)))
+    line = {
+        "impl": "reference", "metric": "fwd+bwd tokens/s per LSTM layer" if cfg["bwd"] else "fwd tokens/s per LSTM layer",
+        "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl, **{k: cfg[k] for k in ("L", "B", "T", "H")}, "cpu_sample_batch": min(CPU_SAMPLE_BATCH[wl], cfg["B"])},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl, cfg = args.workload, WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference(args, wl, cfg)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    import fastlstm_b200 as F
+    from fastlstm_b200 import _lib
+    from fastlstm_b200.sharded import GradBucket, shard_bounds
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the CUDA path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    _lib.check(lib.blstm_device_check(local), "device check")
+
+    dt = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[cfg["dtype"]]
+    L, T, H, Bg = cfg["L"], cfg["T"], cfg["H"], cfg["B"]
+    lo, hi = shard_bounds(Bg, rank, world)
+    B = hi - lo
+    gen = torch.Generator().manual_seed(1000 + int(wl[1]))
+    torch.manual_seed(1000 + int(wl[1]))           # identical weights on every rank
+    model = F.FastLSTM(H, H, num_layers=L, batch_first=cfg["batch_first"], device=dev, dtype=dt)
+    # seeded synthetic inputs; each rank generates only its own rows (seed offset by rank)
+    gen.manual_seed(2000 + 16 * int(wl[1]) + rank)
+    shape = (B, T, H) if cfg["batch_first"] else (T, B, H)
+    x_host = torch.randn(shape, generator=gen).to(dt).pin_memory()
+    dout = torch.randn(shape, generator=gen).to(dt).to(dev)
+    state = None
+    if cfg["h0"] > 0:
+        state = tuple((torch.randn(L, B, H, generator=gen) * cfg["h0"]).to(dt).to(dev) for _ in range(2))
+    x_dev = x_host.to(dev).requires_grad_(cfg["bwd"])
+    hn_host = torch.empty((L, B, H), dtype=dt).pin_memory()
+    bucket = GradBucket(model) if (cfg["bwd"] and world > 1) else None
+
+    def step(x):
+        if cfg["bwd"]:
+            for p in model.parameters():
+                p.grad = None
+            if x.grad is not None:
+                x.grad = None
+            out, (hn, cn) = model(x, state)
+            out.backward(dout)
+            if bucket is not None:
+                bucket.allreduce()
+        else:
+            with torch.no_grad():
+                out, (hn, cn) = model(x, state)
+        return hn
+
+    def e2e_step():
+        x = x_host.to(dev, non_blocking=True).requires_grad_(cfg["bwd"])
+        hn = step(x)
+        hn_host.copy_(hn, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step(x_dev)
+    F.check_status()
+    sampler = ClockSampler(local)
+    sampler.start()
+    n0 = lib.blstm_launch_count()
+    ms_total = timed(lambda: step(x_dev), args.steps)
+    launches = int(lib.blstm_launch_count() - n0)
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    sampler.stop_flag = True
+    sampler.join(2)
+    F.check_status()
+
+    tokens = L * Bg * T                      # layer-tokens per step, whole job
+    ms_step = ms_total / args.steps
+    value = tokens / (ms_step * 1e-3)
+    e2e_value = tokens / (ms_e2e / args.steps * 1e-3)
+
+    # ---- roofline of the dominant kernel: forward recurrence timed alone (rank-local)
+    hbm_gbs, tflops, which = peaks()
+    es = ESIZE[cfg["dtype"]]
+    d = _lib.Desc(_lib.DTYPE_CODE[cfg["dtype"]], T, B, H, H, 0, 0, 0)
+    nws = lib.blstm_workspace_bytes(d, _lib.PHASE_FWD)
+    ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+    pre = (torch.randn(T, B, 4 * H, device=dev) * 0.5).to(dt)
+    ifgo = torch.empty_like(pre)
+    Wh = model.weight_hh_l0.detach()
+    states = torch.zeros(2, T + 1, B, H, device=dev, dtype=dt)
+    st = torch.cuda.current_stream().cuda_stream
+    durs = []
+    for i in range(3 + 5):
+        ifgo.copy_(pre)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.check(lib.blstm_fwd_recurrence(d, ifgo.data_ptr(), Wh.data_ptr(), states[0].data_ptr(),
+                                            states[1].data_ptr(), ws.data_ptr(), nws, st), "fwd_recurrence")
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            durs.append(e0.elapsed_time(e1))
+    rec_ms = sum(durs) / len(durs)
+    alg_bytes = 10.0 * B * H * es * T + 4.0 * H * H * es       # 10*B*H*e per step + Wh once
+    alg_flops = 8.0 * B * H * H * T
+    hbm_time = alg_bytes / (hbm_gbs * 1e9)
+    tensor_time = alg_flops / (tflops * 1e12)
+    if hbm_time >= tensor_time:
+        roof = {"bound": "hbm", "achieved": alg_bytes / (rec_ms * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s"}
+    else:
+        roof = {"bound": "tensor", "achieved": alg_flops / (rec_ms * 1e-3) / 1e12, "peak": tflops, "unit": "TFLOP/s"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof.update({"kernel": "forward recurrence (%s)" % lib.blstm_plan_name(d, 0).decode(),
+                 "peak_source": f"of {which}", "ms_per_launch": rec_ms,
+                 "us_per_timestep": rec_ms * 1e3 / T, "traffic": None})
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            tr = json.load(f).get(f"{wl}_fwd_recurrence")
+        if tr:
+            roof["traffic"] = tr["bytes_per_launch_full"]
+    except Exception:
+        pass
+    del pre, ifgo, states, ws
+
+    line = {
+        "metric": "fwd+bwd tokens/s per LSTM layer" if cfg["bwd"] else "fwd tokens/s per LSTM layer",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": cfg["dtype"], "data": "synthetic",
+        "config": {"workload": wl, "L": L, "B": Bg, "B_per_gpu": B, "T": T, "I": H, "H": H,
+                   "pass": "fwd+bwd" if cfg["bwd"] else "fwd", "sharding": f"batch/{world}",
+                   "collective": "one fp32 sum-allreduce of dWx,dWh,db (NCCL)" if bucket is not None else "none",
+                   "l2": "inputs larger than L2 (no flush needed)" if x_host.numel() * es > 126e6 else "inputs smaller than L2; not flushed",
+                   "plan_fwd": lib.blstm_plan_name(d, 0).decode(), "plan_bwd": lib.blstm_plan_name(d, 1).decode()},
+        "us_per_timestep": ms_step * 1e3 / (T * L),
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": x_host.numel() * es * world,
+                "d2h_bytes_per_step": hn_host.numel() * es * world},
+        "gpu_launches": launches,
+        "clocks": sampler.result(),
+        "roofline": roof,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"], _ = cpu_baseline(wl, cfg)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

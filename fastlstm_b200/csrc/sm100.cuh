@@ -1,0 +1,28 @@
+// Host launchers of the tcgen05/TMEM + TMA kernels (16-bit element types).
+#pragma once
+#include "common.cuh"
+
+namespace blstm {
+
+// true when the tcgen05 GEMMs cover this problem (projection, dgrad, wgrad)
+bool sm100_gemm_supported(const blstm_desc& d);
+// scratch the backward GEMMs need (bytes)
+size_t sm100_bwd_gemm_workspace(const blstm_desc& d);
+
+int sm100_input_projection(const blstm_desc& d, const void* x, const void* Wx, const void* bx,
+                           const void* bh, void* ifgo, cudaStream_t st);
+int sm100_dgrad_input(const blstm_desc& d, const void* d_ifgo, const void* Wx, void* dx, void* ws,
+                      size_t ws_bytes, cudaStream_t st);
+int sm100_wgrad(const blstm_desc& d, const void* d_ifgo, const void* x, const void* out, float* dWx,
+                float* dWh, void* ws, size_t ws_bytes, cudaStream_t st);
+
+// true when the tcgen05 persistent recurrence covers this problem
+bool sm100_recurrence_supported(const blstm_desc& d, int phase);
+size_t sm100_recurrence_workspace(const blstm_desc& d, int phase);
+int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* out, void* cell,
+                         void* ws, size_t ws_bytes, cudaStream_t st);
+int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n, const void* dc_n,
+                         const void* ifgo, const void* cell, const void* Wh, void* d_ifgo, void* dh0,
+                         void* dc0, float* db, void* ws, size_t ws_bytes, cudaStream_t st);
+
+}  // namespace blstm

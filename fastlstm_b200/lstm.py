@@ -1,0 +1,328 @@
+"""Host side of the B200 LSTM layer: the reference's module surface over the C ABI.
+
+Mirrors oleicht/FastLSTM `fastlstm/lstm.py`:
+
+  lstm_persistent_fwd   <- fastlstm/lstm.py:31-146
+  lstm_persistent_bwd   <- fastlstm/lstm.py:236-334
+  Wgrad                 <- fastlstm/lstm.py:494-501
+  PersistentLSTMfn      <- fastlstm/lstm.py:504-538
+  FastLSTM              <- fastlstm/lstm.py:586-698
+
+Differences (all additions): `bias` and `batch_first` constructor arguments,
+gradients through the returned (h_n, c_n), fp32 weight/bias gradients, fp32
+matmuls stay fp32 (the reference flips the global TF32 switch on import,
+fastlstm/lstm.py:15-19; this module does not).  PyTorch is used for device
+memory, streams and autograd only; every device computation goes through
+libfastlstm_b200.so and there is no fallback path.
+"""
+from __future__ import annotations
+
+import os
+import threading
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+
+_DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+# Set FASTLSTM_B200_SYNC_CHECK=1 to read the device status word (and wait for
+# the stream) after every recurrence launch; otherwise it is read lazily.
+_SYNC_CHECK = os.environ.get("FASTLSTM_B200_SYNC_CHECK", "0") == "1"
+_FORCE_GENERIC = os.environ.get("FASTLSTM_B200_FORCE_GENERIC", "0") == "1"
+_WAIT_LIMIT_US = int(os.environ.get("FASTLSTM_B200_WAIT_LIMIT_US", "0"))
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _desc(dtype, T, B, I, H, flags=0):
+    if dtype not in _DTYPE_CODE:
+        raise ValueError(f"unsupported dtype {dtype}; expected float32, float16 or bfloat16")
+    if _FORCE_GENERIC:
+        flags |= _lib.FLAG_FORCE_GENERIC
+    return _lib.Desc(_DTYPE_CODE[dtype], T, B, I, H, flags, _WAIT_LIMIT_US, 0)
+
+
+def _require(t, name, dtype=None, shape=None, device=None):
+    if t is None:
+        return
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if device is not None and t.device != device:
+        raise ValueError(f"{name} is on {t.device}, expected {device}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+# ---------------------------------------------------------------------------
+# Deferred device-status checks: each recurrence launch leaves a status word in
+# its workspace; it is copied to pinned memory on the same stream and examined
+# once the copy has completed (at a later call, or in check_status()).
+# ---------------------------------------------------------------------------
+class _StatusRing:
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.pending = []   # (event, pinned tensor, label)
+        self.free = []
+
+    def push(self, ws, label):
+        with self.lock:
+            host = self.free.pop() if self.free else torch.empty(4, dtype=torch.int32, pin_memory=True)
+        host.copy_(ws[:16].view(torch.int32), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(ws.device))
+        with self.lock:
+            self.pending.append((ev, host, label))
+
+    def poll(self, wait=False):
+        with self.lock:
+            items, self.pending = self.pending, []
+        keep, err = [], None
+        for ev, host, label in items:
+            if wait:
+                ev.synchronize()
+            if ev.query():
+                code = int(host[1])
+                if code != 0 and err is None:
+                    err = (code, label, int(host[2]), int(host[3]))
+                with self.lock:
+                    self.free.append(host)
+            else:
+                keep.append((ev, host, label))
+        with self.lock:
+            self.pending = keep + self.pending
+        if err is not None:
+            code, label, d0, d1 = err
+            raise _lib.BlstmError(code, f"{label} (step {d0}, batch tile {d1})")
+
+
+_status = _StatusRing()
+
+
+def check_status(wait: bool = True):
+    """Raise if any finished launch recorded a device-side error (a bounded wait
+    that ran out).  With wait=True, first waits for all outstanding launches."""
+    _status.poll(wait=wait)
+
+
+def _after_launch(desc, ws, label):
+    if _SYNC_CHECK:
+        rc = _lib.load().blstm_read_status(ws.data_ptr(), None, _stream(ws))
+        _lib.check(rc, label)
+    else:
+        _status.push(ws, label)
+        _status.poll(wait=False)
+
+
+def plan_name(dtype, T, B, I, H, phase="fwd"):
+    """Kernel family ("generic" / "sm100") the library picks for this problem."""
+    d = _desc(dtype, T, B, I, H)
+    return _lib.load().blstm_plan_name(d, _lib.PHASE_FWD if phase == "fwd" else _lib.PHASE_BWD).decode()
+
+
+# ---------------------------------------------------------------------------
+# Operator functions (same names and argument meaning as the reference)
+# ---------------------------------------------------------------------------
+def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh):
+    """Forward of one layer.  x [T,B,I]; h0,c0 [B,H] or None; Wx [4H,I]; Wh [4H,H];
+    bx,bh [4H] or None.  Returns (out[T+1,B,H], cell[T+1,B,H], ifgo[T,B,4H]);
+    slot 0 of out/cell is the initial state.  (fastlstm/lstm.py:31-146)"""
+    lib = _lib.load()
+    if x.dim() == 2:
+        x = x[None]
+    T, B, I = x.shape
+    H = Wh.shape[1]
+    dt, dev = x.dtype, x.device
+    _require(x, "x")
+    _require(Wx, "Wx", dt, (4 * H, I), dev)
+    _require(Wh, "Wh", dt, (4 * H, H), dev)
+    _require(bx, "bx", dt, (4 * H,), dev)
+    _require(bh, "bh", dt, (4 * H,), dev)
+    if (h0 is None) != (c0 is None):
+        raise ValueError("h0 and c0 must both be given or both be None")
+    _require(h0, "h0", dt, (B, H), dev)
+    _require(c0, "c0", dt, (B, H), dev)
+    d = _desc(dt, T, B, I, H)
+    with torch.cuda.device(dev):
+        states = torch.empty((2, T + 1, B, H), device=dev, dtype=dt)
+        out, cell = states.unbind(0)
+        ifgo = torch.empty((T, B, 4 * H), device=dev, dtype=dt)
+        ws_bytes = lib.blstm_workspace_bytes(d, _lib.PHASE_FWD)
+        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        rc = lib.blstm_fwd(d, _ptr(x), _ptr(h0), _ptr(c0), _ptr(Wx), _ptr(Wh), _ptr(bx), _ptr(bh),
+                           _ptr(out), _ptr(cell), _ptr(ifgo), _ptr(ws), ws_bytes, _stream(x))
+        _lib.check(rc, "blstm_fwd")
+        _after_launch(d, ws, "forward recurrence")
+    return out, cell, ifgo
+
+
+def lstm_persistent_bwd(dh, dc_n, dh_n, x, h, cell, ifgo, Wx, Wh, need_dx=True):
+    """Backward of one layer.  dh [T,B,H] gradient of out[1:]; dc_n, dh_n [B,H]
+    (or None) gradients of the final states; h = out[T+1,B,H] from forward.
+    Returns (d_x, dh_0, dc_0, dWx, dbx, dWh, dbh); weight and bias gradients are
+    fp32, dbx is dbh.  (fastlstm/lstm.py:236-334)"""
+    lib = _lib.load()
+    T, B, H = dh.shape
+    I = x.shape[-1]
+    dt, dev = x.dtype, x.device
+    dh = dh.contiguous()
+    _require(dh, "dh", dt, (T, B, H), dev)
+    _require(dh_n, "dh_n", dt, (B, H), dev)
+    _require(dc_n, "dc_n", dt, (B, H), dev)
+    _require(h, "h", dt, (T + 1, B, H), dev)
+    _require(cell, "cell", dt, (T + 1, B, H), dev)
+    _require(ifgo, "ifgo", dt, (T, B, 4 * H), dev)
+    d = _desc(dt, T, B, I, H)
+    with torch.cuda.device(dev):
+        d_ifgo = torch.empty_like(ifgo)
+        d_x = torch.empty((T, B, I), device=dev, dtype=dt) if need_dx else None
+        carries = torch.empty((2, B, H), device=dev, dtype=dt)
+        dh_0, dc_0 = carries.unbind(0)
+        wgrads = torch.empty(4 * H * (I + H + 1), device=dev, dtype=torch.float32)
+        dWx = wgrads[:4 * H * I].view(4 * H, I)
+        dWh = wgrads[4 * H * I:4 * H * (I + H)].view(4 * H, H)
+        db = wgrads[4 * H * (I + H):]
+        ws_bytes = lib.blstm_workspace_bytes(d, _lib.PHASE_BWD)
+        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        rc = lib.blstm_bwd(d, _ptr(dh), _ptr(dh_n), _ptr(dc_n), _ptr(x), _ptr(h), _ptr(cell),
+                           _ptr(ifgo), _ptr(Wx), _ptr(Wh), _ptr(d_ifgo), _ptr(d_x), _ptr(dh_0),
+                           _ptr(dc_0), _ptr(dWx), _ptr(dWh), _ptr(db), _ptr(ws), ws_bytes, _stream(x))
+        _lib.check(rc, "blstm_bwd")
+        _after_launch(d, ws, "backward recurrence")
+    return d_x, dh_0, dc_0, dWx, db, dWh, db
+
+
+def Wgrad(d_ifgo, x, h):
+    """(dbx, dbh, dWx, dWh) from d_ifgo [T,B,4H], x [T,B,I], h = out[T+1,B,H].
+    (fastlstm/lstm.py:494-501; fp32 results, no transpose copy)"""
+    lib = _lib.load()
+    T, B, G = d_ifgo.shape
+    H, I = G // 4, x.shape[-1]
+    d = _desc(x.dtype, T, B, I, H)
+    dev = x.device
+    with torch.cuda.device(dev):
+        dWx = torch.empty((G, I), device=dev, dtype=torch.float32)
+        dWh = torch.empty((G, H), device=dev, dtype=torch.float32)
+        ws_bytes = lib.blstm_workspace_bytes(d, _lib.PHASE_BWD)
+        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        rc = lib.blstm_wgrad(d, _ptr(d_ifgo), _ptr(x), _ptr(h), _ptr(dWx), _ptr(dWh), _ptr(ws),
+                             ws_bytes, _stream(x))
+        _lib.check(rc, "blstm_wgrad")
+        db = d_ifgo.reshape(T * B, G).sum(dim=0, dtype=torch.float32)
+    return db, db, dWx, dWh
+
+
+class PersistentLSTMfn(torch.autograd.Function):
+    """autograd Function of one layer (fastlstm/lstm.py:504-538).
+
+    forward(x, h_0, c_0, Wx, bx, Wh, bh) -> (out[T,B,H], h_n[B,H], c_n[B,H]);
+    unlike the reference, h_n and c_n are flat outputs and differentiable."""
+
+    @staticmethod
+    def forward(ctx, x, h_0, c_0, Wx, bx, Wh, bh):
+        if torch.is_autocast_enabled("cuda"):
+            target = torch.get_autocast_dtype("cuda")
+            x, Wx, Wh = x.to(target), Wx.to(target), Wh.to(target)
+            bx = None if bx is None else bx.to(target)
+            bh = None if bh is None else bh.to(target)
+            h_0 = None if h_0 is None else h_0.to(target)
+            c_0 = None if c_0 is None else c_0.to(target)
+        x = x.contiguous()
+        with torch.autograd.profiler.record_function("fastlstm_b200::fwd"):
+            out, cell, ifgo = lstm_persistent_fwd(
+                x, None if h_0 is None else h_0.contiguous(), None if c_0 is None else c_0.contiguous(),
+                Wx.contiguous(), bx, Wh.contiguous(), bh)
+        ctx.h0_is_none = h_0 is None
+        ctx.has_bias = (bx is not None, bh is not None)
+        ctx.save_for_backward(x, out, cell, ifgo, Wx, Wh)
+        return out[1:], out[-1], cell[-1]
+
+    @staticmethod
+    def backward(ctx, d_out, d_hn, d_cn):
+        x, out, cell, ifgo, Wx, Wh = ctx.saved_tensors
+        T, B, H = out.shape[0] - 1, out.shape[1], out.shape[2]
+        if d_out is None:
+            d_out = torch.zeros((T, B, H), device=x.device, dtype=x.dtype)
+        d_out = d_out.to(x.dtype).contiguous()
+        d_hn = None if d_hn is None else d_hn.to(x.dtype).contiguous()
+        d_cn = None if d_cn is None else d_cn.to(x.dtype).contiguous()
+        with torch.autograd.profiler.record_function("fastlstm_b200::bwd"):
+            d_x, dh_0, dc_0, dWx, dbx, dWh, dbh = lstm_persistent_bwd(
+                d_out, d_cn, d_hn, x, out, cell, ifgo, Wx.contiguous(), Wh.contiguous(),
+                need_dx=ctx.needs_input_grad[0])
+        if ctx.h0_is_none:
+            dh_0 = dc_0 = None
+        return (d_x, dh_0, dc_0, dWx, dbx if ctx.has_bias[0] else None, dWh,
+                dbh if ctx.has_bias[1] else None)
+
+
+def persistent_lstm(x, h_0, c_0, Wx, bx, Wh, bh):
+    """Reference-shaped call: returns (out, (h_n, c_n)) like PersistentLSTMfn.apply
+    does in fastlstm/lstm.py:522."""
+    out, h_n, c_n = PersistentLSTMfn.apply(x, h_0, c_0, Wx, bx, Wh, bh)
+    return out, (h_n, c_n)
+
+
+class FastLSTM(nn.Module):
+    """nn.LSTM-style stacked LSTM on the B200 kernels (fastlstm/lstm.py:586-698).
+
+    Parameters have nn.LSTM's names, shapes, init distribution and RNG order
+    (weight_ih_l{k}, weight_hh_l{k}, bias_ih_l{k}, bias_hh_l{k}), so state dicts
+    are interchangeable with torch.nn.LSTM.  `version` is accepted for source
+    compatibility; only "persistent" exists here."""
+
+    def __init__(self, input_size, hidden_size, num_layers=1, bias=True, batch_first=False,
+                 version="persistent", device=None, dtype=None):
+        super().__init__()
+        if version != "persistent":
+            raise ValueError(f"Not implemented: {version} (only 'persistent' exists)")
+        self.input_size, self.hidden_size, self.num_layers = input_size, hidden_size, num_layers
+        self.bias, self.batch_first, self.version = bias, batch_first, version
+        k = 1.0 / hidden_size ** 0.5
+        fk = dict(device=device, dtype=dtype)
+
+        def u(*shape):
+            return nn.Parameter(torch.rand(*shape, **fk) * 2 * k - k)
+
+        for layer in range(num_layers):
+            setattr(self, f"weight_ih_l{layer}", u(4 * hidden_size, input_size if layer == 0 else hidden_size))
+            setattr(self, f"weight_hh_l{layer}", u(4 * hidden_size, hidden_size))
+            if bias:
+                setattr(self, f"bias_ih_l{layer}", u(4 * hidden_size))
+                setattr(self, f"bias_hh_l{layer}", u(4 * hidden_size))
+
+    def layer_params(self, layer):
+        g = lambda n: getattr(self, f"{n}_l{layer}", None)
+        return g("weight_ih"), g("bias_ih"), g("weight_hh"), g("bias_hh")
+
+    def forward(self, x, h_c_0=None):
+        if x.dim() != 3:
+            raise ValueError("expected a 3-D input [T,B,I] (or [B,T,I] with batch_first)")
+        if self.batch_first:
+            x = x.transpose(0, 1)
+        if h_c_0 is None:
+            h_0 = c_0 = [None] * self.num_layers
+        else:
+            h_0, c_0 = h_c_0
+            if h_0 is None or c_0 is None:
+                raise ValueError("h_c_0 must be a pair (h_0, c_0) of [num_layers, B, H] tensors or None")
+        h_n, c_n = [], []
+        for layer in range(self.num_layers):
+            Wx, bx, Wh, bh = self.layer_params(layer)
+            x, h_i, c_i = PersistentLSTMfn.apply(x, h_0[layer], c_0[layer], Wx, bx, Wh, bh)
+            h_n.append(h_i)
+            c_n.append(c_i)
+        if self.batch_first:
+            x = x.transpose(0, 1)
+        return x, (torch.stack(h_n), torch.stack(c_n))
