@@ -1,0 +1,419 @@
+// tcgen05/TMEM + TMA GEMM for the dense contractions of the LSTM layer
+// (16-bit operands, fp32 accumulation in tensor memory):
+//
+//   input projection  ifgo = x * Wx^T + (bx+bh)     A K-major,  B K-major,  16-bit out
+//   input gradient    dx   = d_ifgo * Wx            A K-major,  B N-major,  16-bit out
+//   weight gradients  dW   = d_ifgo^T * [x | h]     A M-major,  B N-major,  fp32 out, split-K
+//
+// They replace the cuBLAS calls of the reference (fastlstm/lstm.py:66-68, :294,
+// :494-501); the M/N-major operand forms remove the reference's transpose copy
+// of d_ifgo (lstm.py:495).
+//
+// One persistent CTA per SM walks 128x256 output tiles.  Warp 0 feeds a 4-stage
+// shared-memory ring with TMA tile loads, warp 1 issues tcgen05.mma into one of
+// two 256-column TMEM accumulators, warps 2-5 drain the other accumulator
+// (tcgen05.ld -> registers -> bias/convert -> global), so the epilogue of tile
+// i overlaps the main loop of tile i+1.  No TMA multicast is used.
+#include "sm100.cuh"
+#include "sm100_common.cuh"
+
+namespace blstm {
+namespace sm100 {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr size_t GEMM_SMEM = 1024 /*align slack*/ + (size_t)STAGES * STAGE_BYTES + 256;
+
+struct GemmParams {
+  int M, N, K;
+  int m_tiles, n_tiles, splits;
+  int kb_total, kb_per_split;
+  int fmt;                 // 0 f16, 1 bf16
+  void* out;               // 16-bit [M,ldc] or fp32 [splits][M,ldc]
+  long long ldc;
+  const void* bias0;       // 16-bit [N] or null
+  const void* bias1;
+  Control* ctl;            // may be null
+  unsigned long long limit_ns;
+};
+
+template <typename T16>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <typename T16> __device__ __forceinline__ float2 unpack2(uint32_t v);
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+
+// A_MN / B_MN: operand is M/N-major in global memory (and therefore in shared memory).
+// OUT_F32: fp32 output (weight gradients), else 16-bit output with optional bias.
+template <int A_MN, int B_MN, bool OUT_F32, typename T16>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                   // [STAGES]
+  uint64_t* empty = bars + STAGES;         // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;  // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    *dead = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = p.m_tiles * p.n_tiles * p.splits;
+  WaitCtx wc{dead, p.ctl, p.limit_ns, -1, (int)blockIdx.x};
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int nt = tile % p.n_tiles, mt = (tile / p.n_tiles) % p.m_tiles, z = tile / (p.n_tiles * p.m_tiles);
+        const int m0 = mt * BM, n0 = nt * BN;
+        const int kb0 = z * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
+          uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN) {
+            tma_load_2d(sa, &tmA, &full[s], m0, k0);
+            tma_load_2d(sa + 8192, &tmA, &full[s], m0 + 64, k0);
+          } else {
+            tma_load_2d(sa, &tmA, &full[s], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[s], n0 + 64 * j, k0);
+          } else {
+            tma_load_2d(sb, &tmB, &full[s], k0, n0);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint64_t descA = A_MN ? smem_desc_base(8192, 1024) : smem_desc_base(16, 1024);
+      constexpr uint64_t descB = B_MN ? smem_desc_base(8192, 1024) : smem_desc_base(16, 1024);
+      constexpr uint32_t stepA = A_MN ? 2048 : 32, stepB = B_MN ? 2048 : 32;  // bytes per K=16
+      const uint32_t idesc = instr_desc(p.fmt, A_MN, B_MN, BM, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t acc_ph[2] = {0, 0};
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+        const int z = tile / (p.n_tiles * p.m_tiles);
+        const int kb0 = z * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+        const int a = it & 1;
+        if (!mbar_wait(&acc_empty[a], acc_ph[a] ^ 1, wc)) { ok = false; break; }
+        acc_ph[a] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_f16(d_tmem, smem_desc(descA, sa + k * stepA), smem_desc(descB, sb + k * stepB), idesc,
+                     (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);   // frees the stage once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&acc_full[a]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                  // TMEM lane quarter this warp may access
+    const int row_in_tile = q * 32 + lane;
+    uint32_t acc_ph[2] = {0, 0};
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+      const int nt = tile % p.n_tiles, mt = (tile / p.n_tiles) % p.m_tiles, z = tile / (p.n_tiles * p.m_tiles);
+      const int m0 = mt * BM, n0 = nt * BN;
+      const int a = it & 1;
+      if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
+      acc_ph[a] ^= 1;
+      tc_fence_after();
+      const int row = m0 + row_in_tile;
+      const uint32_t taddr = tmem_base + a * BN + (uint32_t(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col = n0 + c;
+        if (row < p.M && col < p.N) {
+          if (OUT_F32) {
+            float* dst = reinterpret_cast<float*>(p.out) + ((size_t)z * p.M + row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col + j < p.N)
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            }
+          } else {
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+              if (col + 2 * j < p.N) {
+                if (p.bias0) {
+                  float2 b = unpack2<T16>(*reinterpret_cast<const uint32_t*>(
+                      reinterpret_cast<const T16*>(p.bias0) + col + 2 * j));
+                  v0 += b.x; v1 += b.y;
+                }
+                if (p.bias1) {
+                  float2 b = unpack2<T16>(*reinterpret_cast<const uint32_t*>(
+                      reinterpret_cast<const T16*>(p.bias1) + col + 2 * j));
+                  v0 += b.x; v1 += b.y;
+                }
+              }
+              o[j] = pack2<T16>(v0, v1);
+            }
+            T16* dst = reinterpret_cast<T16*>(p.out) + (size_t)row * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col + 8 * j < p.N)
+                *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[a]);
+    }
+  }
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// fp32 [splits][n] partials -> out[n] (deterministic order)
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, size_t n, float* __restrict__ out) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 s = *reinterpret_cast<const float4*>(part + i);
+  for (int z = 1; z < splits; ++z) {
+    const float4 v = *reinterpret_cast<const float4*>(part + (size_t)z * n + i);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  *reinterpret_cast<float4*>(out + i) = s;
+}
+
+// ---------------------------------------------------------------- host
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+int encode_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeFn fn = get_encode_fn();
+  if (!fn) {
+    set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point unavailable");
+    return BLSTM_E_CUDA;
+  }
+  cuuint64_t gdim[5], gstr[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx,
+                  es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled rejected the tensor map");
+    return BLSTM_E_CUDA;
+  }
+  return BLSTM_OK;
+}
+
+// Operand description: row-major 16-bit matrix [rows, cols] with leading dimension ld (elements).
+// K-major operand: rows = M or N, cols = K.  MN-major operand: rows = K, cols = M or N.
+static int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                            bool mn_major, int tile_mn) {
+  uint64_t dims[2] = {cols, rows};
+  uint64_t str[1] = {ld * 2};
+  uint32_t box[2];
+  if (mn_major) { box[0] = 64; box[1] = BK; }            // 64 M/N elements x 64 k rows per box
+  else          { box[0] = BK; box[1] = (uint32_t)tile_mn; }
+  return encode_tensor_map(map, base, 2, dims, str, box);
+}
+
+template <int A_MN, int B_MN, bool OUT_F32, typename T16>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sm_count, cudaStream_t st) {
+  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32, T16>;
+  BLSTM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
+  const int tiles = p.m_tiles * p.n_tiles * p.splits;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ta, tb, p);
+  BLSTM_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return BLSTM_OK;
+}
+
+// C[M,N] = op(A) * op(B).  A: K-major [M,K] (lda) or M-major [K,M] (lda); B: K-major [N,K] or
+// N-major [K,N].  out: 16-bit [M,ldc] (+bias) or fp32.  splits > 1 needs `partials`
+// (fp32 [splits][M][ldc]) and writes the reduced result to out.
+int gemm(int dtype, int M, int N, int K, const void* A, long long lda, bool a_mn, const void* B, long long ldb,
+         bool b_mn, void* out, long long ldc, bool out_f32, const void* bias0, const void* bias1, int splits,
+         float* partials, Control* ctl, cudaStream_t st) {
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc) return rc;
+  CUtensorMap ta, tb;
+  rc = a_mn ? make_operand_map(&ta, A, K, M, lda, true, BM) : make_operand_map(&ta, A, M, K, lda, false, BM);
+  if (rc) return rc;
+  rc = b_mn ? make_operand_map(&tb, B, K, N, ldb, true, BN) : make_operand_map(&tb, B, N, K, ldb, false, BN);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.m_tiles = cdiv(M, BM); p.n_tiles = cdiv(N, BN);
+  p.kb_total = cdiv(K, BK);
+  if (splits < 1) splits = 1;
+  if (splits > p.kb_total) splits = p.kb_total;
+  p.kb_per_split = cdiv(p.kb_total, splits);
+  p.splits = cdiv(p.kb_total, p.kb_per_split);
+  p.fmt = dtype == BLSTM_BF16 ? 1 : 0;
+  p.out = (p.splits > 1) ? (void*)partials : out;
+  p.ldc = ldc;
+  p.bias0 = bias0; p.bias1 = bias1;
+  p.ctl = ctl;
+  p.limit_ns = kDefaultWaitNs;
+  if (p.splits > 1 && (!out_f32 || !partials)) return BLSTM_E_INVALID_ARG;
+#define BLSTM_GEMM_CASE(AM, BMN, F32)                                                              \
+  if (a_mn == (AM != 0) && b_mn == (BMN != 0) && out_f32 == F32) {                                 \
+    rc = (dtype == BLSTM_BF16) ? launch<AM, BMN, F32, __nv_bfloat16>(ta, tb, p, di.sm_count, st)   \
+                               : launch<AM, BMN, F32, __half>(ta, tb, p, di.sm_count, st);         \
+  } else
+  BLSTM_GEMM_CASE(0, 0, false)
+  BLSTM_GEMM_CASE(0, 1, false)
+  BLSTM_GEMM_CASE(1, 1, true)
+  { return BLSTM_E_UNSUPPORTED; }
+#undef BLSTM_GEMM_CASE
+  if (rc) return rc;
+  if (p.splits > 1) {
+    const size_t n = (size_t)M * ldc;
+    splitk_reduce_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(partials, p.splits, n, (float*)out);
+    BLSTM_CUDA_OK(cudaGetLastError());
+    count_launch();
+  }
+  return BLSTM_OK;
+}
+
+// ---------------------------------------------------------------- LSTM-level wrappers
+static int pick_splits(int M, int N, int K, int sm_count) {
+  const int tiles = cdiv(M, BM) * cdiv(N, BN);
+  if (tiles >= sm_count) return 1;
+  int s = sm_count / tiles;
+  const int kb = cdiv(K, BK);
+  if (s > kb / 8) s = kb / 8;       // keep at least 8 k-blocks per split
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+}  // namespace sm100
+
+using namespace sm100;
+
+bool sm100_gemm_supported(const blstm_desc& d) {
+  if (d.flags & BLSTM_FLAG_FORCE_GENERIC) return false;
+  if (d.dtype != BLSTM_F16 && d.dtype != BLSTM_BF16) return false;
+  // 16-byte row pitches for TMA and 16-byte vector stores in the epilogues
+  return d.input_size % 8 == 0 && d.hidden_size % 8 == 0;
+}
+
+static int wgrad_splits(const blstm_desc& d, int N) {
+  return pick_splits(4 * d.hidden_size, N, d.seq_len * d.batch, 148);
+}
+
+size_t sm100_bwd_gemm_workspace(const blstm_desc& d) {
+  const size_t G = 4 * (size_t)d.hidden_size;
+  const int sx = wgrad_splits(d, d.input_size), sh = wgrad_splits(d, d.hidden_size);
+  size_t a = sx > 1 ? (size_t)sx * G * d.input_size * 4 : 0;
+  size_t b = sh > 1 ? (size_t)sh * G * d.hidden_size * 4 : 0;
+  return round_up(a > b ? a : b, 256);
+}
+
+int sm100_input_projection(const blstm_desc& d, const void* x, const void* Wx, const void* bx, const void* bh,
+                           void* ifgo, cudaStream_t st) {
+  const int M = d.seq_len * d.batch, N = 4 * d.hidden_size, K = d.input_size;
+  return gemm(d.dtype, M, N, K, x, K, false, Wx, K, false, ifgo, N, false, bx, bh, 1, nullptr, nullptr, st);
+}
+
+int sm100_dgrad_input(const blstm_desc& d, const void* d_ifgo, const void* Wx, void* dx, void* ws, size_t ws_bytes,
+                      cudaStream_t st) {
+  (void)ws; (void)ws_bytes;
+  const int M = d.seq_len * d.batch, N = d.input_size, K = 4 * d.hidden_size;
+  return gemm(d.dtype, M, N, K, d_ifgo, K, false, Wx, N, true, dx, N, false, nullptr, nullptr, 1, nullptr, nullptr, st);
+}
+
+int sm100_wgrad(const blstm_desc& d, const void* d_ifgo, const void* x, const void* out, float* dWx, float* dWh,
+                void* ws, size_t ws_bytes, cudaStream_t st) {
+  const int TB = d.seq_len * d.batch, G = 4 * d.hidden_size, I = d.input_size, H = d.hidden_size;
+  if (ws_bytes < sm100_bwd_gemm_workspace(d)) return BLSTM_E_WORKSPACE;
+  int rc = gemm(d.dtype, G, I, TB, d_ifgo, G, true, x, I, true, dWx, I, true, nullptr, nullptr, wgrad_splits(d, I),
+                (float*)ws, nullptr, st);
+  if (rc) return rc;
+  return gemm(d.dtype, G, H, TB, d_ifgo, G, true, out, H, true, dWh, H, true, nullptr, nullptr, wgrad_splits(d, H),
+              (float*)ws, nullptr, st);
+}
+
+}  // namespace blstm
