@@ -103,6 +103,21 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// TMA store of one shared-memory box to global memory (bulk async-group completion).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// wait until all but the N most recent store groups have finished READING shared memory
+template <int N> __device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// wait until all but the N most recent store groups have fully completed
+template <int N> __device__ __forceinline__ void tma_store_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -179,10 +194,11 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt, int a_mn, int b_mn, i
 }
 
 // ---------------------------------------------------------------- host: tensor maps
-// 2-D/3-D tiled map over a dense 16-bit tensor, 128-byte swizzle, zero fill out of range.
-// dims/strides are given innermost first; strides (bytes) for dims 1.. only.
+// Tiled map over a dense tensor of 2-byte (elem_bytes = 2) or 4-byte elements, 128-byte
+// swizzle, zero fill out of range.  dims/strides are given innermost first; strides (bytes)
+// for dims 1.. only.
 int encode_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box);
+                      const uint64_t* strides_bytes, const uint32_t* box, int elem_bytes = 2);
 
 }  // namespace sm100
 }  // namespace blstm

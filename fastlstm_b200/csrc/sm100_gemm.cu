@@ -26,7 +26,10 @@ constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 192;
-constexpr size_t GEMM_SMEM = 1024 /*align slack*/ + (size_t)STAGES * STAGE_BYTES + 256;
+constexpr int STG_BYTES = 4096;        // one epilogue staging box: 32 rows x 128 B
+constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;   // 4 epilogue warps, double-buffered
+constexpr size_t GEMM_SMEM = 1024 /*align slack*/ + (size_t)STAGES * STAGE_BYTES + STG_TOTAL + 128 + BN * 4;
+static_assert(GEMM_SMEM <= 232448, "exceeds the 227 KB shared-memory limit per CTA");
 
 struct GemmParams {
   int M, N, K;
@@ -40,6 +43,13 @@ struct GemmParams {
   Control* ctl;            // may be null
   unsigned long long limit_ns;
 };
+
+#ifdef BLSTM_GEMM_TRACE
+__device__ long long g_trace[16384];
+#define TRACE(i, v) do { if (blockIdx.x == 0 && (i) < 16384) g_trace[(i)] = (v); } while (0)
+#else
+#define TRACE(i, v) do { } while (0)
+#endif
 
 template <typename T16>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -64,16 +74,18 @@ template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v)
 template <int A_MN, int B_MN, bool OUT_F32, typename T16>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
+  uint8_t* staging = smem + (size_t)STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + STG_TOTAL);
   uint64_t* full = bars;                   // [STAGES]
   uint64_t* empty = bars + STAGES;         // [STAGES]
   uint64_t* acc_full = bars + 2 * STAGES;  // [2]
   uint64_t* acc_empty = acc_full + 2;      // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* bias_s = reinterpret_cast<float*>(bars) + 32;   // [BN] fp32, 128 B past the barriers
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -83,6 +95,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
@@ -141,12 +154,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int z = tile / (p.n_tiles * p.m_tiles);
         const int kb0 = z * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
         const int a = it & 1;
+        TRACE(it * 8 + 0, (long long)globaltimer_ns());
         if (!mbar_wait(&acc_empty[a], acc_ph[a] ^ 1, wc)) { ok = false; break; }
         acc_ph[a] ^= 1;
+        TRACE(it * 8 + 1, (long long)globaltimer_ns());
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
+          if (kb == kb0) TRACE(it * 8 + 2, (long long)globaltimer_ns());
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -159,13 +175,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit(&acc_full[a]);
+        TRACE(it * 8 + 3, (long long)globaltimer_ns());
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                  // TMEM lane quarter this warp may access
-    const int row_in_tile = q * 32 + lane;
     uint32_t acc_ph[2] = {0, 0};
+    uint32_t stg_toggle = 0;
+    const bool has_bias = !OUT_F32 && (p.bias0 != nullptr || p.bias1 != nullptr);
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
@@ -174,55 +192,81 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int a = it & 1;
       if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
       acc_ph[a] ^= 1;
+      if (warp == 2 && lane == 0) TRACE(it * 8 + 4, (long long)globaltimer_ns());
       tc_fence_after();
-      const int row = m0 + row_in_tile;
-      const uint32_t taddr = tmem_base + a * BN + (uint32_t(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c, r);
-        tmem_ld_wait();
-        const int col = n0 + c;
-        if (row < p.M && col < p.N) {
-          if (OUT_F32) {
-            float* dst = reinterpret_cast<float*>(p.out) + ((size_t)z * p.M + row) * p.ldc + col;
+      if (has_bias) {
+        // fp32 sum of the two bias vectors for this tile's 256 columns (zero past N), staged
+        // once per tile by the 128 epilogue threads
+        const int t128 = threadIdx.x - 64;
+        float* bdst = bias_s;
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // previous tile's readers are done
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (col + j < p.N)
-                *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-            }
-          } else {
-            uint32_t o[16];
+        for (int j = 0; j < 2; ++j) {
+          const int cc = n0 + t128 * 2 + j;
+          float b = 0.f;
+          if (cc < p.N) {
+            if (p.bias0) b += Elem<T16>::to_f(reinterpret_cast<const T16*>(p.bias0)[cc]);
+            if (p.bias1) b += Elem<T16>::to_f(reinterpret_cast<const T16*>(p.bias1)[cc]);
+          }
+          bdst[t128 * 2 + j] = b;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      const uint32_t taddr = tmem_base + a * BN + (uint32_t(q * 32) << 16);
+      constexpr int CW = OUT_F32 ? 32 : 64;      // output columns per staged box (128 B per row)
+      uint8_t* my_stage = staging + (warp - 2) * 2 * STG_BYTES;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += CW) {
+        const int col = n0 + c;
+        if (col >= p.N) break;
+        uint32_t v[32];
+        if (OUT_F32) {
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+        } else {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + c, r0);
+          tmem_ld_32x32(taddr + c + 32, r1);
+          tmem_ld_wait();
+          if (has_bias) {
+            const float2* bs = reinterpret_cast<const float2*>(bias_s + c);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
-              if (col + 2 * j < p.N) {
-                if (p.bias0) {
-                  float2 b = unpack2<T16>(*reinterpret_cast<const uint32_t*>(
-                      reinterpret_cast<const T16*>(p.bias0) + col + 2 * j));
-                  v0 += b.x; v1 += b.y;
-                }
-                if (p.bias1) {
-                  float2 b = unpack2<T16>(*reinterpret_cast<const uint32_t*>(
-                      reinterpret_cast<const T16*>(p.bias1) + col + 2 * j));
-                  v0 += b.x; v1 += b.y;
-                }
-              }
-              o[j] = pack2<T16>(v0, v1);
+              const float2 b0 = bs[j], b1 = bs[16 + j];
+              v[j] = pack2<T16>(__uint_as_float(r0[2 * j]) + b0.x, __uint_as_float(r0[2 * j + 1]) + b0.y);
+              v[16 + j] = pack2<T16>(__uint_as_float(r1[2 * j]) + b1.x, __uint_as_float(r1[2 * j + 1]) + b1.y);
             }
-            T16* dst = reinterpret_cast<T16*>(p.out) + (size_t)row * p.ldc + col;
+          } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (col + 8 * j < p.N)
-                *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            for (int j = 0; j < 16; ++j) {
+              v[j] = pack2<T16>(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+              v[16 + j] = pack2<T16>(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
             }
           }
+        }
+        // stage the 32x128-byte box with the 128-byte swizzle the output tensor map expects,
+        // then one lane hands it to TMA (rows/columns past M/N are clipped by the hardware)
+        uint8_t* buf = my_stage + (stg_toggle & 1) * STG_BYTES;
+        ++stg_toggle;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&tmC, buf, col, m0 + q * 32, z);
+          tma_store_commit();
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[a]);
+      if (warp == 2 && lane == 0) TRACE(it * 8 + 5, (long long)globaltimer_ns());
     }
+    if (lane == 0) tma_store_wait<0>();
   }
   // ------------------------------------------------------------ teardown
   tc_fence_before();
@@ -265,7 +309,7 @@ static EncodeFn get_encode_fn() {
 }
 
 int encode_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box) {
+                      const uint64_t* strides_bytes, const uint32_t* box, int elem_bytes) {
   EncodeFn fn = get_encode_fn();
   if (!fn) {
     set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point unavailable");
@@ -275,7 +319,7 @@ int encode_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64
   cuuint32_t bx[5], es[5];
   for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
   for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx,
+  CUresult r = fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx,
                   es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -298,12 +342,13 @@ static int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, u
 }
 
 template <int A_MN, int B_MN, bool OUT_F32, typename T16>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sm_count, cudaStream_t st) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                  int sm_count, cudaStream_t st) {
   auto kern = gemm_kernel<A_MN, B_MN, OUT_F32, T16>;
   BLSTM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
   const int tiles = p.m_tiles * p.n_tiles * p.splits;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ta, tb, p);
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ta, tb, tc, p);
   BLSTM_CUDA_OK(cudaGetLastError());
   count_launch();
   return BLSTM_OK;
@@ -338,10 +383,19 @@ int gemm(int dtype, int M, int N, int K, const void* A, long long lda, bool a_mn
   p.ctl = ctl;
   p.limit_ns = kDefaultWaitNs;
   if (p.splits > 1 && (!out_f32 || !partials)) return BLSTM_E_INVALID_ARG;
+  CUtensorMap tc;
+  {
+    const int eb = out_f32 ? 4 : 2;
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)p.splits};
+    uint64_t str[2] = {(uint64_t)ldc * eb, (uint64_t)M * ldc * eb};
+    uint32_t box[3] = {out_f32 ? 32u : 64u, 32u, 1u};
+    rc = encode_tensor_map(&tc, p.out, 3, dims, str, box, eb);
+    if (rc) return rc;
+  }
 #define BLSTM_GEMM_CASE(AM, BMN, F32)                                                              \
   if (a_mn == (AM != 0) && b_mn == (BMN != 0) && out_f32 == F32) {                                 \
-    rc = (dtype == BLSTM_BF16) ? launch<AM, BMN, F32, __nv_bfloat16>(ta, tb, p, di.sm_count, st)   \
-                               : launch<AM, BMN, F32, __half>(ta, tb, p, di.sm_count, st);         \
+    rc = (dtype == BLSTM_BF16) ? launch<AM, BMN, F32, __nv_bfloat16>(ta, tb, tc, p, di.sm_count, st)   \
+                               : launch<AM, BMN, F32, __half>(ta, tb, tc, p, di.sm_count, st);         \
   } else
   BLSTM_GEMM_CASE(0, 0, false)
   BLSTM_GEMM_CASE(0, 1, false)
@@ -370,6 +424,12 @@ static int pick_splits(int M, int N, int K, int sm_count) {
 }
 
 }  // namespace sm100
+
+#ifdef BLSTM_GEMM_TRACE
+extern "C" int blstm_dbg_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, sm100::g_trace, sizeof(long long) * n);
+}
+#endif
 
 using namespace sm100;
 
