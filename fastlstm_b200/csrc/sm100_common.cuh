@@ -56,7 +56,7 @@ struct WaitCtx {
 };
 
 // Bounded mbarrier wait.  Returns false when the CTA (or the grid) has given up.
-__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
+static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   unsigned spins = 0;

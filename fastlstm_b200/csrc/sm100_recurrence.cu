@@ -1,0 +1,430 @@
+// Persistent tcgen05 recurrence kernels for 16-bit LSTM layers.
+//
+// Forward (replaces persistent_fwd_kernel, fastlstm/kernels.py:414-663):
+//   CTA (pb, ht) owns UH hidden units (their 4 gate rows of Wh: N = 4*UH rows, all
+//   K = H columns) and keeps that slice RESIDENT in shared memory for the whole
+//   sequence.  Per (timestep, batch tile of 128 rows) it computes
+//       D[128, N] = h[t][tile rows, :] (TMA-streamed, K-major)  x  Wh_slice^T
+//   with tcgen05.mma into a TMEM accumulator, then the epilogue warps add the
+//   projected pre-activations, write the final pre-activations back (saved for
+//   backward), apply the gates with c carried in fp32 registers, and publish
+//   h[t+1] / c[t+1].  h is exchanged between the CTAs of a batch tile through
+//   global memory (L2): one arrival counter per (timestep, batch tile), released
+//   by every epilogue warp and acquired (bounded spin) by the TMA producer of each
+//   CTA before it streams h[t+1].  Each CTA interleaves up to two independent
+//   batch tiles so the hand-off latency of one hides behind the math of the other.
+//
+//   warp 0      TMA producer (flag wait, h tiles, Wh slice once)
+//   warp 1      tcgen05.mma issuer, TMEM owner
+//   warps 2..   epilogue: thread = batch row, 16 hidden units x 4 gates per thread
+#include "sm100.cuh"
+#include "sm100_common.cuh"
+
+namespace blstm {
+namespace sm100 {
+
+constexpr int RB = 128;                 // batch rows per tile (MMA M)
+constexpr int RK = 64;                  // K chunk (one 128-byte swizzle row)
+constexpr int R_STAGES = 4;
+constexpr int R_STAGE_BYTES = RB * RK * 2;   // 16 KB
+
+struct RecPlan {
+  bool ok;
+  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads;
+  size_t w_bytes, smem;
+  size_t off_flags, n_flags, ws_bytes;
+};
+
+// Geometry is a pure function of the problem (no device query): 148 SMs assumed, the
+// cooperative launch refuses if the device cannot hold the grid.
+static RecPlan make_plan(const blstm_desc& d, int phase) {
+  RecPlan p{};
+  p.ok = false;
+  if (d.flags & BLSTM_FLAG_FORCE_GENERIC) return p;
+  if (phase != BLSTM_PHASE_FWD) return p;
+  if (d.dtype != BLSTM_F16 && d.dtype != BLSTM_BF16) return p;
+  const int H = d.hidden_size, B = d.batch;
+  if (H % 64 != 0 || H < 64 || H > 1024) return p;
+  p.nbt = cdiv(B, RB);
+  int UH = 16;
+  if (H <= 512 && p.nbt * (H / 32) >= 74) UH = 32;   // enough tiles to fill the GPU with wider slices
+  p.UH = UH;
+  p.N = 4 * UH;
+  p.nh = H / UH;
+  if (p.nh > 148) return p;
+  p.nb_par = 148 / p.nh;
+  if (p.nb_par > p.nbt) p.nb_par = p.nbt;
+  p.ntl = cdiv(p.nbt, p.nb_par);
+  p.TI = p.ntl >= 2 ? 2 : 1;
+  p.grid = p.nh * p.nb_par;
+  p.epi_warps = 4 * (UH / 16);
+  p.threads = 64 + 32 * p.epi_warps;
+  p.w_bytes = (size_t)p.N * H * 2;
+  p.smem = 1024 + p.w_bytes + (size_t)R_STAGES * R_STAGE_BYTES + 256;
+  if (p.smem > 232448) return p;
+  p.n_flags = (size_t)(d.seq_len + 1) * p.nbt;
+  p.off_flags = sizeof(Control);
+  p.ws_bytes = p.off_flags + round_up(p.n_flags * sizeof(int), 256);
+  p.ok = true;
+  return p;
+}
+
+struct FwdParams {
+  int T, B, H;
+  int nbt, nh, nb_par, ntl;
+  int fmt;
+  int no_arrive;
+  int flag_target;          // nh * epilogue warps
+  unsigned long long limit_ns;
+  Control* ctl;
+  int* flags;
+  void* ifgo;               // [T,B,4H] in/out
+  void* out;                // [T+1,B,H]
+  void* cell;               // [T+1,B,H]
+};
+
+template <typename T16> __device__ __forceinline__ float2 cvt2(uint32_t v);
+template <> __device__ __forceinline__ float2 cvt2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+template <> __device__ __forceinline__ float2 cvt2<__nv_bfloat16>(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+template <typename T16> __device__ __forceinline__ uint32_t pk2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pk2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pk2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ uint4 ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void stg16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+
+// UH: hidden units per CTA (16 or 32).  TI: batch tiles interleaved per CTA (1 or 2).
+template <int UH, int TI, typename T16>
+__global__ void __launch_bounds__(64 + 128 * (UH / 16), 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmH, const FwdParams p) {
+  constexpr int N = 4 * UH;
+  constexpr int EW = 4 * (UH / 16);                 // epilogue warps
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int H = p.H;
+  const int KC = H / RK;                            // K chunks
+  uint8_t* w_s = smem;                              // [KC][N rows][128 B]
+  uint8_t* a_s = smem + (size_t)N * H * 2;          // [R_STAGES][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * R_STAGE_BYTES);
+  uint64_t* full = bars;                            // [R_STAGES]
+  uint64_t* empty = bars + R_STAGES;                // [R_STAGES]
+  uint64_t* acc_full = bars + 2 * R_STAGES;         // [2]
+  uint64_t* acc_empty = acc_full + 2;               // [2]
+  uint64_t* w_full = acc_empty + 2;                 // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 1);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ht = blockIdx.x % p.nh, pb = blockIdx.x / p.nh;
+  constexpr uint32_t TMEM_COLS = (2 * N <= 128) ? 128 : ((2 * N <= 256) ? 256 : 512);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EW); }
+    mbar_init(w_full, 1);
+    *dead = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmH);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wc{dead, p.ctl, p.limit_ns, -1, (int)blockIdx.x};
+
+  // Work items of this CTA, in the order every role walks them:
+  //   for chunk (TI tiles) : for t in [0,T) : for j in [0,TI) : (t, bt = pb + (chunk*TI + j) * nb_par)
+  const int n_chunks = (p.ntl + TI - 1) / TI;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      // resident Wh slice: rows (gate g, unit ht*UH + u), all K, as KC chunks of [N][64]
+      mbar_expect_tx(w_full, (uint32_t)((size_t)N * H * 2));
+      for (int kc = 0; kc < KC; ++kc) tma_load_3d(w_s + (size_t)kc * N * 128, &tmW, w_full, kc * RK, ht * UH, 0);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int ch = 0; ch < n_chunks && ok; ++ch) {
+        for (int t = 0; t < p.T && ok; ++t) {
+          for (int j = 0; j < TI && ok; ++j) {
+            const int bt = pb + (ch * TI + j) * p.nb_par;
+            if (bt >= p.nbt) continue;
+            if (t > 0) {   // h[t] of this batch tile complete: every epilogue warp of every hidden tile arrived
+              wc.d0 = t; wc.d1 = bt;
+              if (!wait_flag_ge(&p.flags[(size_t)t * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, t, bt)) {
+                *dead = 1; ok = false; break;
+              }
+              fence_proxy_async();   // peers' generic-proxy stores -> this thread's async-proxy (TMA) reads
+            }
+            for (int kc = 0; kc < KC; ++kc) {
+              if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
+              mbar_expect_tx(&full[s], R_STAGE_BYTES);
+              tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmH, &full[s], kc * RK, bt * RB, t);
+              if (++s == R_STAGES) { s = 0; ph ^= 1; }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint64_t descK = smem_desc_base(16, 1024);
+      const uint32_t idesc = instr_desc(p.fmt, 0, 0, RB, N);
+      bool ok = mbar_wait(w_full, 0, wc);
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t acc_ph[2] = {0, 0};
+      int it = 0;
+      const uint32_t w_addr = smem_u32(w_s);
+      for (int ch = 0; ch < n_chunks && ok; ++ch) {
+        for (int t = 0; t < p.T && ok; ++t) {
+          for (int j = 0; j < TI && ok; ++j) {
+            const int bt = pb + (ch * TI + j) * p.nb_par;
+            if (bt >= p.nbt) continue;
+            const int a = it & 1;
+            ++it;
+            if (!mbar_wait(&acc_empty[a], acc_ph[a] ^ 1, wc)) { ok = false; break; }
+            acc_ph[a] ^= 1;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + a * N;
+            for (int kc = 0; kc < KC; ++kc) {
+              if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES);
+              const uint32_t sb = w_addr + (uint32_t)kc * N * 128;
+#pragma unroll
+              for (int k = 0; k < RK / 16; ++k)
+                umma_f16(d_tmem, smem_desc(descK, sa + k * 32), smem_desc(descK, sb + k * 32), idesc,
+                         (kc > 0 || k > 0) ? 1u : 0u);
+              umma_commit(&empty[s]);
+              if (++s == R_STAGES) { s = 0; ph ^= 1; }
+            }
+            if (ok) umma_commit(&acc_full[a]);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - 2;
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int ug = ew >> 2;                 // which 16-unit group of the CTA's UH units
+    const int row_in_tile = q * 32 + lane;
+    const int unit0 = ht * UH + ug * 16;
+    const size_t H4 = 4 * (size_t)H;
+    T16* ifgo = reinterpret_cast<T16*>(p.ifgo);
+    T16* out = reinterpret_cast<T16*>(p.out);
+    T16* cell = reinterpret_cast<T16*>(p.cell);
+    uint32_t acc_ph[2] = {0, 0};
+    int it = 0;
+    bool ok = true;
+    for (int ch = 0; ch < n_chunks && ok; ++ch) {
+      float c[TI][16];
+      uint4 pre[8];                         // projected pre-activations of the NEXT item: 4 gates x 16 units
+      // initial cell state of this chunk's tiles
+#pragma unroll
+      for (int j = 0; j < TI; ++j) {
+        const int bt = pb + (ch * TI + j) * p.nb_par;
+        const int row = bt * RB + row_in_tile;
+        if (bt < p.nbt && row < p.B) {
+          const uint4 v0 = ldg16(cell + (size_t)row * H + unit0), v1 = ldg16(cell + (size_t)row * H + unit0 + 8);
+          const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+          for (int u = 0; u < 8; ++u) { const float2 f = cvt2<T16>(w[u]); c[j][2 * u] = f.x; c[j][2 * u + 1] = f.y; }
+        } else {
+#pragma unroll
+          for (int u = 0; u < 16; ++u) c[j][u] = 0.f;
+        }
+      }
+      // prefetch pre-activations of the first item
+      {
+        const int bt = pb + (ch * TI) * p.nb_par;
+        const int row = bt * RB + row_in_tile;
+        if (bt < p.nbt && row < p.B) {
+          const T16* src = ifgo + (size_t)row * H4 + unit0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) { pre[2 * g] = ldg16(src + (size_t)g * H); pre[2 * g + 1] = ldg16(src + (size_t)g * H + 8); }
+        }
+      }
+      for (int t = 0; t < p.T && ok; ++t) {
+#pragma unroll
+        for (int j = 0; j < TI; ++j) {
+          const int bt = pb + (ch * TI + j) * p.nb_par;
+          if (bt >= p.nbt) continue;
+          const int a = it & 1;
+          ++it;
+          const int row = bt * RB + row_in_tile;
+          const bool row_ok = row < p.B;
+          wc.d0 = t; wc.d1 = bt;
+          if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
+          acc_ph[a] ^= 1;
+          tc_fence_after();
+          const uint32_t taddr = tmem_base + a * N + (uint32_t(q * 32) << 16) + ug * 16;
+          uint32_t acc[4][16];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) tmem_ld_32x16(taddr + g * UH, acc[g]);
+          tmem_ld_wait();
+          // the accumulator is in registers: hand the TMEM buffer back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[a]);
+
+          float pa[4][16];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t w[8] = {pre[2 * g].x, pre[2 * g].y, pre[2 * g].z, pre[2 * g].w,
+                                   pre[2 * g + 1].x, pre[2 * g + 1].y, pre[2 * g + 1].z, pre[2 * g + 1].w};
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const float2 f = cvt2<T16>(w[u]);
+              pa[g][2 * u] = __uint_as_float(acc[g][2 * u]) + f.x;
+              pa[g][2 * u + 1] = __uint_as_float(acc[g][2 * u + 1]) + f.y;
+            }
+          }
+          // issue the NEXT item's pre-activation loads now; they land while this item finishes
+          {
+            int nj = j + 1, nt = t;
+            if (nj == TI || pb + (ch * TI + nj) * p.nb_par >= p.nbt) { nj = 0; nt = t + 1; }
+            const int nbt_ = pb + (ch * TI + nj) * p.nb_par;
+            const int nrow = nbt_ * RB + row_in_tile;
+            if (nt < p.T && nrow < p.B) {
+              const T16* src = ifgo + ((size_t)nt * p.B + nrow) * H4 + unit0;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) { pre[2 * g] = ldg16(src + (size_t)g * H); pre[2 * g + 1] = ldg16(src + (size_t)g * H + 8); }
+            }
+          }
+          if (row_ok) {
+            T16* gdst = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint32_t w[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) w[u] = pk2<T16>(pa[g][2 * u], pa[g][2 * u + 1]);
+              stg16(gdst + (size_t)g * H, make_uint4(w[0], w[1], w[2], w[3]));
+              stg16(gdst + (size_t)g * H + 8, make_uint4(w[4], w[5], w[6], w[7]));
+            }
+            float hv[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+              const float cn = sigmoid_fast(pa[1][u]) * c[j][u] + sigmoid_fast(pa[0][u]) * tanh_fast(pa[2][u]);
+              c[j][u] = cn;
+              hv[u] = sigmoid_fast(pa[3][u]) * tanh_fast(cn);
+            }
+            uint32_t wc_[8], wh_[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              wc_[u] = pk2<T16>(c[j][2 * u], c[j][2 * u + 1]);
+              wh_[u] = pk2<T16>(hv[2 * u], hv[2 * u + 1]);
+            }
+            const size_t o1 = ((size_t)(t + 1) * p.B + row) * H + unit0;
+            stg16(cell + o1, make_uint4(wc_[0], wc_[1], wc_[2], wc_[3]));
+            stg16(cell + o1 + 8, make_uint4(wc_[4], wc_[5], wc_[6], wc_[7]));
+            stg16(out + o1, make_uint4(wh_[0], wh_[1], wh_[2], wh_[3]));
+            stg16(out + o1 + 8, make_uint4(wh_[4], wh_[5], wh_[6], wh_[7]));
+          }
+          // publish: this warp's rows of h[t+1] are written; peers read them through TMA
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && !p.no_arrive) {
+            __threadfence();
+            red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
+          }
+        }
+      }
+    }
+  }
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int UH, int TI, typename T16>
+static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensorMap& th, FwdParams& p,
+                        cudaStream_t st) {
+  auto kern = fwd_kernel<UH, TI, T16>;
+  BLSTM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+  void* args[] = {(void*)&tw, (void*)&th, (void*)&p};
+  BLSTM_CUDA_OK(cudaLaunchCooperativeKernel((void*)kern, dim3(pl.grid), dim3(pl.threads), args, pl.smem, st));
+  count_launch();
+  return BLSTM_OK;
+}
+
+}  // namespace sm100
+
+using namespace sm100;
+
+bool sm100_recurrence_supported(const blstm_desc& d, int phase) { return make_plan(d, phase).ok; }
+size_t sm100_recurrence_workspace(const blstm_desc& d, int phase) { return make_plan(d, phase).ws_bytes; }
+
+int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* out, void* cell, void* ws,
+                         size_t ws_bytes, cudaStream_t st) {
+  const RecPlan pl = make_plan(d, BLSTM_PHASE_FWD);
+  if (!pl.ok) return BLSTM_E_UNSUPPORTED;
+  if (ws_bytes < pl.ws_bytes) return BLSTM_E_WORKSPACE;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc) return rc;
+  if (!di.coop || pl.grid > di.sm_count) return BLSTM_E_NOT_CORESIDENT;
+  const int H = d.hidden_size, B = d.batch, T = d.seq_len;
+  CUtensorMap tw, th;
+  {  // Wh [4H,H] as {k, unit row, gate}
+    uint64_t dims[3] = {(uint64_t)H, (uint64_t)H, 4};
+    uint64_t str[2] = {(uint64_t)H * 2, (uint64_t)H * H * 2};
+    uint32_t box[3] = {RK, (uint32_t)pl.UH, 4};
+    rc = encode_tensor_map(&tw, Wh, 3, dims, str, box);
+    if (rc) return rc;
+  }
+  {  // out [T+1,B,H] as {k, batch row, t}: rows past B are zero-filled, never another timestep
+    uint64_t dims[3] = {(uint64_t)H, (uint64_t)B, (uint64_t)(T + 1)};
+    uint64_t str[2] = {(uint64_t)H * 2, (uint64_t)B * H * 2};
+    uint32_t box[3] = {RK, RB, 1};
+    rc = encode_tensor_map(&th, out, 3, dims, str, box);
+    if (rc) return rc;
+  }
+  BLSTM_CUDA_OK(cudaMemsetAsync(ws, 0, pl.ws_bytes, st));
+  FwdParams p;
+  p.T = T; p.B = B; p.H = H;
+  p.nbt = pl.nbt; p.nh = pl.nh; p.nb_par = pl.nb_par; p.ntl = pl.ntl;
+  p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
+  p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
+  p.flag_target = pl.nh * pl.epi_warps;
+  p.limit_ns = d.wait_limit_us > 0 ? (unsigned long long)d.wait_limit_us * 1000ull : kDefaultWaitNs;
+  p.ctl = reinterpret_cast<Control*>(ws);
+  p.flags = reinterpret_cast<int*>(static_cast<char*>(ws) + pl.off_flags);
+  p.ifgo = ifgo; p.out = out; p.cell = cell;
+  const bool bf = d.dtype == BLSTM_BF16;
+#define BLSTM_FWD_CASE(U, I)                                                                         \
+  if (pl.UH == U && pl.TI == I)                                                                      \
+    return bf ? launch_fwd_t<U, I, __nv_bfloat16>(pl, tw, th, p, st) : launch_fwd_t<U, I, __half>(pl, tw, th, p, st);
+  BLSTM_FWD_CASE(16, 1)
+  BLSTM_FWD_CASE(16, 2)
+  BLSTM_FWD_CASE(32, 1)
+  BLSTM_FWD_CASE(32, 2)
+#undef BLSTM_FWD_CASE
+  return BLSTM_E_UNSUPPORTED;
+}
+
+int sm100_bwd_recurrence(const blstm_desc&, const void*, const void*, const void*, const void*, const void*,
+                         const void*, void*, void*, void*, float*, void*, size_t, cudaStream_t) {
+  return BLSTM_E_UNSUPPORTED;
+}
+
+}  // namespace blstm

@@ -1,0 +1,92 @@
+"""tcgen05 persistent recurrence kernels through the C ABI against the CUDA-core kernels
+(same inputs, force flag) and against an fp32 step-by-step torch evaluation."""
+import pytest
+import torch
+
+from fastlstm_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+TD = {"fp16": torch.float16, "bf16": torch.bfloat16}
+
+# (T, B, H): single tile; ragged batch tile; several hidden tiles; H=1024 slices; wide slices +
+# interleaved tiles (UH=32, TI=2); ragged with interleave
+FWD_SHAPES = [(3, 128, 64), (5, 200, 128), (8, 256, 256), (4, 64, 1024), (6, 1300, 512), (4, 2304, 256),
+              (40, 96, 256)]
+
+
+def _desc(dtype, T, B, H, flags=0):
+    return _lib.Desc(_lib.DTYPE_CODE[dtype], T, B, H, H, flags, 0, 0)
+
+
+def _fwd(lib, d, pre, Wh, h0, c0):
+    T, B, H = d.seq_len, d.batch, d.hidden_size
+    ifgo = pre.clone()
+    st = torch.zeros(2, T + 1, B, H, device="cuda", dtype=pre.dtype)
+    st[0, 0], st[1, 0] = h0, c0
+    n = lib.blstm_workspace_bytes(d, _lib.PHASE_FWD)
+    ws = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.blstm_fwd_recurrence(d, ifgo.data_ptr(), Wh.data_ptr(), st[0].data_ptr(), st[1].data_ptr(),
+                                        ws.data_ptr(), n, s), "fwd_recurrence")
+    _lib.check(lib.blstm_read_status(ws.data_ptr(), None, s), "status")
+    return ifgo, st[0], st[1]
+
+
+def _torch_fwd(pre, Wh, h0, c0):
+    """fp32 math with h fed back at storage precision (what both kernels do)."""
+    T, B, G = pre.shape
+    H = G // 4
+    dt = pre.dtype
+    W = Wh.float()
+    h, c = h0.float(), c0.float()
+    outs, cells, gates = [], [], []
+    for t in range(T):
+        a = pre[t].float() + h @ W.T
+        gates.append(a)
+        i, f, g, o = a.split(H, dim=1)
+        c = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(g)
+        h = (torch.sigmoid(o) * torch.tanh(c)).to(dt).float()
+        outs.append(h)
+        cells.append(c)
+    return torch.stack(gates), torch.stack(outs), torch.stack(cells)
+
+
+def _cmp(name, got, ref, atol):
+    err = (got.float() - ref.float()).abs()
+    if float(err.max()) > atol:
+        idx = (err > atol).nonzero()
+        first = idx[0].tolist()
+        rows = sorted(set(idx[:, -2].tolist()))
+        cols = sorted(set(idx[:, -1].tolist()))
+        ts = sorted(set(idx[:, 0].tolist()))
+        pytest.fail(f"{name}: max err {float(err.max()):.4g} > {atol}; {idx.shape[0]}/{err.numel()} bad; first {first} "
+                    f"got {float(got[tuple(first)]):.5g} want {float(ref[tuple(first)]):.5g}; t {ts[:6]} "
+                    f"rows {rows[:6]}..{rows[-1]} cols {cols[:6]}..{cols[-1]}")
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("shape", FWD_SHAPES)
+def test_forward_recurrence(dtype, shape):
+    lib = _lib.load()
+    T, B, H = shape
+    dt = TD[dtype]
+    g = torch.Generator(device="cuda").manual_seed(B + H)
+    pre = (torch.randn(T, B, 4 * H, generator=g, device="cuda")).to(dt)
+    Wh = ((torch.rand(4 * H, H, generator=g, device="cuda") * 2 - 1) / H ** 0.5).to(dt)
+    h0 = (torch.randn(B, H, generator=g, device="cuda") * 0.3).to(dt)
+    c0 = (torch.randn(B, H, generator=g, device="cuda") * 0.3).to(dt)
+    d = _desc(dtype, T, B, H)
+    assert lib.blstm_plan_name(d, 0) == b"sm100"
+    ifgo, out, cell = _fwd(lib, d, pre, Wh, h0, c0)
+    rg, ro, rc = _torch_fwd(pre, Wh, h0, c0)
+    tol = 4e-3 if dtype == "fp16" else 3e-2
+    _cmp("ifgo", ifgo, rg, tol * 4)
+    _cmp("out", out[1:], ro, tol)
+    _cmp("cell", cell[1:], rc, tol * 2)
+    # and against the CUDA-core kernels
+    ifgo2, out2, cell2 = _fwd(lib, _desc(dtype, T, B, H, _lib.FLAG_FORCE_GENERIC), pre, Wh, h0, c0)
+    _cmp("out vs generic", out, out2, tol)
+    _cmp("cell vs generic", cell, cell2, tol * 2)
+    # bit-identical when repeated
+    ifgo3, out3, _ = _fwd(lib, d, pre, Wh, h0, c0)
+    assert torch.equal(out, out3) and torch.equal(ifgo, ifgo3)
