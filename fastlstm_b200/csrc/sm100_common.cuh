@@ -56,8 +56,7 @@ struct WaitCtx {
 };
 
 // Bounded mbarrier wait.  Returns false when the CTA (or the grid) has given up.
-static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
-  if (mbar_try_wait(bar, parity)) return true;
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
   const unsigned long long t0 = globaltimer_ns();
   unsigned spins = 0;
   for (;;) {
@@ -78,6 +77,12 @@ static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, co
       }
     }
   }
+}
+
+// Fast path inline (single-thread producer / issuer loops are instruction-latency bound).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, w);
 }
 
 // ---------------------------------------------------------------- fences

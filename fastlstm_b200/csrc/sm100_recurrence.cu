@@ -25,12 +25,19 @@ namespace sm100 {
 
 constexpr int RB = 128;                 // batch rows per tile (MMA M)
 constexpr int RK = 64;                  // K chunk (one 128-byte swizzle row)
-constexpr int R_STAGES = 4;
+constexpr int R_MAX_STAGES = 8;
 constexpr int R_STAGE_BYTES = RB * RK * 2;   // 16 KB
+
+#ifdef BLSTM_REC_TRACE
+__device__ long long g_rtrace[16384];
+#define RTRACE(i, v) do { if (blockIdx.x == 0 && (i) < 16384) g_rtrace[(i)] = (v); } while (0)
+#else
+#define RTRACE(i, v) do { } while (0)
+#endif
 
 struct RecPlan {
   bool ok;
-  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads;
+  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages;
   size_t w_bytes, smem;
   size_t off_flags, n_flags, ws_bytes;
 };
@@ -58,10 +65,13 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.TI = p.ntl >= 2 ? 2 : 1;
   p.grid = p.nh * p.nb_par;
   p.epi_warps = 4 * (UH / 16);
-  p.threads = 64 + 32 * p.epi_warps;
+  p.threads = 32 * (1 + 256 / p.N + p.epi_warps);   // producer + MMA issuers + epilogue
   p.w_bytes = (size_t)p.N * H * 2;
-  p.smem = 1024 + p.w_bytes + (size_t)R_STAGES * R_STAGE_BYTES + 256;
-  if (p.smem > 232448) return p;
+  const size_t fixed = 1024 + p.w_bytes + 256;
+  if (fixed + 2 * R_STAGE_BYTES > 232448) return p;
+  p.stages = (int)((232448 - fixed) / R_STAGE_BYTES);
+  if (p.stages > R_MAX_STAGES) p.stages = R_MAX_STAGES;
+  p.smem = fixed + (size_t)p.stages * R_STAGE_BYTES;
   p.n_flags = (size_t)(d.seq_len + 1) * p.nbt;
   p.off_flags = sizeof(Control);
   p.ws_bytes = p.off_flags + round_up(p.n_flags * sizeof(int), 256);
@@ -72,6 +82,7 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
 struct FwdParams {
   int T, B, H;
   int nbt, nh, nb_par, ntl;
+  int stages;
   int fmt;
   int no_arrive;
   int flag_target;          // nh * epilogue warps
@@ -105,7 +116,7 @@ __device__ __forceinline__ void stg16(void* p, uint4 v) { *reinterpret_cast<uint
 
 // UH: hidden units per CTA (16 or 32).  TI: batch tiles interleaved per CTA (1 or 2).
 template <int UH, int TI, typename T16>
-__global__ void __launch_bounds__(64 + 128 * (UH / 16), 1)
+__global__ void __launch_bounds__(32 * (1 + 256 / (4 * UH) + 4 * (UH / 16)), 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmH, const FwdParams p) {
   constexpr int N = 4 * UH;
   constexpr int EW = 4 * (UH / 16);                 // epilogue warps
@@ -114,11 +125,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   const int H = p.H;
   const int KC = H / RK;                            // K chunks
   uint8_t* w_s = smem;                              // [KC][N rows][128 B]
-  uint8_t* a_s = smem + (size_t)N * H * 2;          // [R_STAGES][128 rows][128 B]
+  const int R_STAGES = p.stages;
+  uint8_t* a_s = smem + (size_t)N * H * 2;          // [stages][128 rows][128 B]
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * R_STAGE_BYTES);
-  uint64_t* full = bars;                            // [R_STAGES]
-  uint64_t* empty = bars + R_STAGES;                // [R_STAGES]
-  uint64_t* acc_full = bars + 2 * R_STAGES;         // [2]
+  uint64_t* full = bars;                            // [R_MAX_STAGES]
+  uint64_t* empty = bars + R_MAX_STAGES;            // [R_MAX_STAGES]
+  uint64_t* acc_full = bars + 2 * R_MAX_STAGES;     // [2]
   uint64_t* acc_empty = acc_full + 2;               // [2]
   uint64_t* w_full = acc_empty + 2;                 // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 1);
@@ -126,11 +138,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ht = blockIdx.x % p.nh, pb = blockIdx.x / p.nh;
-  constexpr uint32_t TMEM_COLS = (2 * N <= 128) ? 128 : ((2 * N <= 256) ? 256 : 512);
+  // One thread can issue a tcgen05.mma only every ~150 clocks whatever its shape, far below
+  // what these small-N shapes need, so NACC warps issue concurrently: warp x takes the x-th
+  // K=16 slice(s) of every chunk into its own TMEM accumulator, and the epilogue adds them up.
+  constexpr int NACC = 256 / N;                     // 4 for N=64, 2 for N=128
+  constexpr int FIRST_EPI = 1 + NACC;               // first epilogue warp
+  constexpr int ACC_STRIDE = NACC * N;              // columns per item buffer (256)
+  constexpr uint32_t TMEM_COLS = 512;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EW); }
+    for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NACC); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], NACC); mbar_init(&acc_empty[a], EW); }
     mbar_init(w_full, 1);
     *dead = 0;
     fence_mbar_init();
@@ -167,20 +185,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               if (!wait_flag_ge(&p.flags[(size_t)t * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, t, bt)) {
                 *dead = 1; ok = false; break;
               }
+              RTRACE(t * 8 + 0, (long long)clock64());
               fence_proxy_async();   // peers' generic-proxy stores -> this thread's async-proxy (TMA) reads
+              RTRACE(t * 8 + 1, (long long)clock64());
             }
+            // single-thread loop: kept free of divisions and calls (issue latency is the limit)
+            const int row0 = bt * RB;
             for (int kc = 0; kc < KC; ++kc) {
               if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
               mbar_expect_tx(&full[s], R_STAGE_BYTES);
-              tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmH, &full[s], kc * RK, bt * RB, t);
+              tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmH, &full[s], kc * RK, row0, t);
               if (++s == R_STAGES) { s = 0; ph ^= 1; }
             }
           }
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp < FIRST_EPI) {
+    // ---------------------------------------------------------------- MMA issuers
+    const int x = warp - 1;                 // accumulator / K-slice index of this issuer
     if (lane == 0) {
       constexpr uint64_t descK = smem_desc_base(16, 1024);
       const uint32_t idesc = instr_desc(p.fmt, 0, 0, RB, N);
@@ -200,27 +223,32 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (!mbar_wait(&acc_empty[a], acc_ph[a] ^ 1, wc)) { ok = false; break; }
             acc_ph[a] ^= 1;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + a * N;
-            for (int kc = 0; kc < KC; ++kc) {
+            const uint32_t d_tmem = tmem_base + a * ACC_STRIDE;
+            for (int kk = 0; kk < KC; ++kk) {
+              const int kc = kk;
               if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
+              if (kk == 0) RTRACE(t * 8 + 2, (long long)clock64());
+              if (t == 100) RTRACE(8192 + kk * 2, (long long)clock64());
               tc_fence_after();
               const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES);
               const uint32_t sb = w_addr + (uint32_t)kc * N * 128;
 #pragma unroll
-              for (int k = 0; k < RK / 16; ++k)
-                umma_f16(d_tmem, smem_desc(descK, sa + k * 32), smem_desc(descK, sb + k * 32), idesc,
-                         (kc > 0 || k > 0) ? 1u : 0u);
+              for (int k = x; k < RK / 16; k += NACC)
+                umma_f16(d_tmem + x * N, smem_desc(descK, sa + k * 32), smem_desc(descK, sb + k * 32), idesc,
+                         (kk > 0 || k >= NACC) ? 1u : 0u);
               umma_commit(&empty[s]);
+              if (t == 100) RTRACE(8192 + kk * 2 + 1, (long long)clock64());
               if (++s == R_STAGES) { s = 0; ph ^= 1; }
             }
             if (ok) umma_commit(&acc_full[a]);
+            RTRACE(t * 8 + 3, (long long)clock64());
           }
         }
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int ew = warp - 2;
+    const int ew = warp - FIRST_EPI;
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int ug = ew >> 2;                 // which 16-unit group of the CTA's UH units
     const int row_in_tile = q * 32 + lane;
@@ -272,17 +300,31 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           wc.d0 = t; wc.d1 = bt;
           if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
           acc_ph[a] ^= 1;
+          if (ew == 0 && lane == 0) RTRACE(t * 8 + 4, (long long)clock64());
           tc_fence_after();
-          const uint32_t taddr = tmem_base + a * N + (uint32_t(q * 32) << 16) + ug * 16;
+          const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16) + ug * 16;
           uint32_t acc[4][16];
 #pragma unroll
           for (int g = 0; g < 4; ++g) tmem_ld_32x16(taddr + g * UH, acc[g]);
           tmem_ld_wait();
+#pragma unroll
+          for (int x = 1; x < NACC; ++x) {
+            uint32_t part[4][16];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) tmem_ld_32x16(taddr + x * N + g * UH, part[g]);
+            tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+#pragma unroll
+              for (int u = 0; u < 16; ++u)
+                acc[g][u] = __float_as_uint(__uint_as_float(acc[g][u]) + __uint_as_float(part[g][u]));
+          }
           // the accumulator is in registers: hand the TMEM buffer back to the MMA warp
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[a]);
 
+          if (ew == 0 && lane == 0) RTRACE(t * 8 + 5, (long long)clock64());
           float pa[4][16];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -295,7 +337,30 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               pa[g][2 * u + 1] = __uint_as_float(acc[g][2 * u + 1]) + f.y;
             }
           }
-          // issue the NEXT item's pre-activation loads now; they land while this item finishes
+          float hv[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const float cn = sigmoid_fast(pa[1][u]) * c[j][u] + sigmoid_fast(pa[0][u]) * tanh_fast(pa[2][u]);
+            c[j][u] = cn;
+            hv[u] = sigmoid_fast(pa[3][u]) * tanh_fast(cn);
+          }
+          const size_t o1 = ((size_t)(t + 1) * p.B + row) * H + unit0;
+          if (row_ok) {
+            uint32_t wh_[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) wh_[u] = pk2<T16>(hv[2 * u], hv[2 * u + 1]);
+            stg16(out + o1, make_uint4(wh_[0], wh_[1], wh_[2], wh_[3]));
+            stg16(out + o1 + 8, make_uint4(wh_[4], wh_[5], wh_[6], wh_[7]));
+          }
+          // publish h[t+1] first (it is all the peers wait for): generic-proxy stores -> proxy fence ->
+          // warp-level arrival with release semantics; peers read the rows through TMA
+          if (ew == 0 && lane == 0) RTRACE(t * 8 + 6, (long long)clock64());
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
+          if (ew == 0 && lane == 0) RTRACE(t * 8 + 7, (long long)clock64());
+          // only now (after the release: a fence would otherwise wait for these loads) fetch the NEXT
+          // item's projected pre-activations; they land while the peers run their step
           {
             int nj = j + 1, nt = t;
             if (nj == TI || pb + (ch * TI + nj) * p.nb_par >= p.nbt) { nj = 0; nt = t + 1; }
@@ -307,6 +372,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               for (int g = 0; g < 4; ++g) { pre[2 * g] = ldg16(src + (size_t)g * H); pre[2 * g + 1] = ldg16(src + (size_t)g * H + 8); }
             }
           }
+          // off the critical path: final pre-activations and c[t+1], saved for backward
           if (row_ok) {
             T16* gdst = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
 #pragma unroll
@@ -317,31 +383,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               stg16(gdst + (size_t)g * H, make_uint4(w[0], w[1], w[2], w[3]));
               stg16(gdst + (size_t)g * H + 8, make_uint4(w[4], w[5], w[6], w[7]));
             }
-            float hv[16];
+            uint32_t wc_[8];
 #pragma unroll
-            for (int u = 0; u < 16; ++u) {
-              const float cn = sigmoid_fast(pa[1][u]) * c[j][u] + sigmoid_fast(pa[0][u]) * tanh_fast(pa[2][u]);
-              c[j][u] = cn;
-              hv[u] = sigmoid_fast(pa[3][u]) * tanh_fast(cn);
-            }
-            uint32_t wc_[8], wh_[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              wc_[u] = pk2<T16>(c[j][2 * u], c[j][2 * u + 1]);
-              wh_[u] = pk2<T16>(hv[2 * u], hv[2 * u + 1]);
-            }
-            const size_t o1 = ((size_t)(t + 1) * p.B + row) * H + unit0;
+            for (int u = 0; u < 8; ++u) wc_[u] = pk2<T16>(c[j][2 * u], c[j][2 * u + 1]);
             stg16(cell + o1, make_uint4(wc_[0], wc_[1], wc_[2], wc_[3]));
             stg16(cell + o1 + 8, make_uint4(wc_[4], wc_[5], wc_[6], wc_[7]));
-            stg16(out + o1, make_uint4(wh_[0], wh_[1], wh_[2], wh_[3]));
-            stg16(out + o1 + 8, make_uint4(wh_[4], wh_[5], wh_[6], wh_[7]));
-          }
-          // publish: this warp's rows of h[t+1] are written; peers read them through TMA
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0 && !p.no_arrive) {
-            __threadfence();
-            red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
           }
         }
       }
@@ -368,6 +414,12 @@ static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensor
 }
 
 }  // namespace sm100
+
+#ifdef BLSTM_REC_TRACE
+extern "C" int blstm_dbg_rtrace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, sm100::g_rtrace, sizeof(long long) * n);
+}
+#endif
 
 using namespace sm100;
 
@@ -403,6 +455,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   FwdParams p;
   p.T = T; p.B = B; p.H = H;
   p.nbt = pl.nbt; p.nh = pl.nh; p.nb_par = pl.nb_par; p.ntl = pl.ntl;
+  p.stages = pl.stages;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
   p.flag_target = pl.nh * pl.epi_warps;
