@@ -47,6 +47,44 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// ---------------------------------------------------------------- thread-block clusters / DSMEM
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t raddr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+// arrive (release, cluster scope) on an mbarrier that lives in a peer CTA's shared memory
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t remote_bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Whole-cluster rendezvous (hardware barrier, unbounded): used only where every CTA of the
+// cluster is certain to arrive - right after launch and as the very last step before exit.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // State every role of a CTA shares for giving up: `dead` lives in shared memory.
 struct WaitCtx {
   volatile int* dead;             // shared-memory flag, set once any wait of this CTA gave up
@@ -61,6 +99,31 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
   unsigned spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*w.dead) return false;
+      if (w.ctl && ld_relaxed_gpu(&w.ctl->abort) != 0) { *w.dead = 1; return false; }
+      if (globaltimer_ns() - t0 > w.limit_ns) {
+        *w.dead = 1;
+        if (w.ctl) {
+          if (atomicCAS(&w.ctl->status, 0, BLSTM_E_WAIT_TIMEOUT) == 0) {
+            w.ctl->detail[0] = w.d0;
+            w.ctl->detail[1] = w.d1;
+          }
+          atomicExch(&w.ctl->abort, 1);
+        }
+        return false;
+      }
+    }
+  }
+}
+
+// Bounded wait with cluster-scope acquire (data delivered by peers' st.shared::cluster).
+static __device__ __noinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  for (;;) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
       if (*w.dead) return false;
       if (w.ctl && ld_relaxed_gpu(&w.ctl->abort) != 0) { *w.dead = 1; return false; }

@@ -17,6 +17,7 @@
 //   warp 0      TMA producer (flag wait, h tiles, Wh slice once)
 //   warp 1      tcgen05.mma issuer, TMEM owner
 //   warps 2..   epilogue: thread = batch row, 16 hidden units x 4 gates per thread
+#include "generic.cuh"
 #include "sm100.cuh"
 #include "sm100_common.cuh"
 
@@ -413,6 +414,435 @@ static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensor
   return BLSTM_OK;
 }
 
+
+// =====================================================================================
+// Backward (replaces lstm_persistent_seq_bwd, fastlstm/kernels.py:1201-1409)
+//
+// dh_{t-1}[B,H] = d_ifgo[t][B,4H] x Wh[4H,H] has K = 4H.  A cluster of four CTAs owns 64
+// output units of one batch tile; CTA r of the cluster takes gate r's K range (H rows of
+// Wh, resident in shared memory as an N-major operand) and streams the matching H columns
+// of d_ifgo[t] through TMA.  Each CTA ends a step with a partial [128 x 64] fp32 product in
+// TMEM; the four partials are reduce-scattered through distributed shared memory (each CTA
+// receives the three 16-unit slices it needs, 24 KB per step) so that CTA r finishes with
+// dh for units [16r, 16r+16) of the cluster's 64 - the units whose gate maths it then
+// does (thread = batch row: dc carried in fp32 registers, d_ifgo[t-1] written and
+// published with the same per-(step, batch tile) arrival counters as the forward kernel).
+// =====================================================================================
+constexpr int DB_PARTS = 64;              // row groups of the bias-gradient column sum
+constexpr int XSLOT_BYTES = RB * 16 * 4;  // one received slice: 128 rows x 16 fp32
+
+struct BwdPlan {
+  bool ok;
+  int nug, nbt, nb_par, ntl, TI, grid, threads, stages;
+  size_t w_bytes, recv_bytes, smem;
+  size_t off_flags, n_flags, off_db, ws_bytes;
+};
+
+static BwdPlan make_bwd_plan(const blstm_desc& d) {
+  BwdPlan p{};
+  p.ok = false;
+  if (d.flags & BLSTM_FLAG_FORCE_GENERIC) return p;
+  if (d.dtype != BLSTM_F16 && d.dtype != BLSTM_BF16) return p;
+  const int H = d.hidden_size, B = d.batch;
+  if (H % 64 != 0 || H < 64 || H > 1024) return p;
+  p.nbt = cdiv(B, RB);
+  p.nug = H / 64;
+  const int per_tile = p.nug * 4;
+  if (per_tile > 148) return p;
+  p.nb_par = 148 / per_tile;
+  if (p.nb_par > p.nbt) p.nb_par = p.nbt;
+  p.ntl = cdiv(p.nbt, p.nb_par);
+  p.TI = p.ntl >= 2 ? 2 : 1;
+  p.grid = p.nb_par * per_tile;
+  p.threads = 32 * (1 + 4 + 4);
+  p.w_bytes = (size_t)H * 128;
+  p.recv_bytes = (size_t)p.TI * 3 * XSLOT_BYTES;
+  const size_t fixed = 1024 + p.w_bytes + p.recv_bytes + 256;
+  if (fixed + 2 * R_STAGE_BYTES > 232448) return p;
+  p.stages = (int)((232448 - fixed) / R_STAGE_BYTES);
+  if (p.stages > R_MAX_STAGES) p.stages = R_MAX_STAGES;
+  p.smem = fixed + (size_t)p.stages * R_STAGE_BYTES;
+  p.n_flags = (size_t)d.seq_len * p.nbt;
+  p.off_flags = sizeof(Control);
+  p.off_db = p.off_flags + round_up(p.n_flags * sizeof(int), 256);
+  p.ws_bytes = p.off_db + round_up((size_t)DB_PARTS * 4 * H * sizeof(float), 256);
+  p.ok = true;
+  return p;
+}
+
+struct BwdParams {
+  int T, B, H;
+  int nbt, nug, nb_par, ntl;
+  int stages;
+  int fmt;
+  int no_arrive;
+  int flag_target;          // (H/16) CTAs per batch tile x 4 epilogue warps
+  unsigned long long limit_ns;
+  Control* ctl;
+  int* flags;               // [T][nbt]: arrivals for d_ifgo[t]
+  const void* dout;         // [T,B,H]
+  const void* dh_n;         // [B,H] or null
+  const void* dc_n;         // [B,H] or null
+  const void* ifgo;         // [T,B,4H]
+  const void* cell;         // [T+1,B,H]
+  void* d_ifgo;             // [T,B,4H]
+  void* dh0;                // [B,H]
+  void* dc0;                // [B,H]
+};
+
+template <typename T16>
+__device__ __forceinline__ void unpack16(const uint4& v0, const uint4& v1, float (&f)[16]) {
+  const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+  for (int u = 0; u < 8; ++u) { const float2 t = cvt2<T16>(w[u]); f[2 * u] = t.x; f[2 * u + 1] = t.y; }
+}
+template <typename T16>
+__device__ __forceinline__ void store16(T16* dst, const float (&f)[16]) {
+  uint32_t w[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) w[u] = pk2<T16>(f[2 * u], f[2 * u + 1]);
+  stg16(dst, make_uint4(w[0], w[1], w[2], w[3]));
+  stg16(dst + 8, make_uint4(w[4], w[5], w[6], w[7]));
+}
+
+template <int TI, typename T16>
+__global__ void __launch_bounds__(288, 1)
+bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, const BwdParams p) {
+  constexpr int N = 64, NACC = 4, ACC_STRIDE = 256;
+  constexpr int FIRST_EPI = 5, EW = 4;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int H = p.H;
+  const int KC = H / RK;
+  const int R_STAGES = p.stages;
+  uint8_t* w_s = smem;                                        // [KC][64 k rows][128 B]
+  float* recv = reinterpret_cast<float*>(smem + (size_t)H * 128);   // [TI][3][128][16]
+  uint8_t* a_s = reinterpret_cast<uint8_t*>(recv) + (size_t)TI * 3 * XSLOT_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * R_STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + R_MAX_STAGES;
+  uint64_t* acc_full = bars + 2 * R_MAX_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint64_t* w_full = acc_empty + 2;
+  uint64_t* xchg = w_full + 1;                                // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xchg + 2);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t r = cluster_ctarank();                       // gate whose K range this CTA owns
+  const int cid = blockIdx.x >> 2;
+  const int ugc = cid % p.nug, pb = cid / p.nug;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NACC); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], NACC); mbar_init(&acc_empty[a], EW); }
+    mbar_init(w_full, 1);
+    for (int j = 0; j < 2; ++j) mbar_init(&xchg[j], 3 * EW);
+    *dead = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmG);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  cluster_sync_all();                 // peers' barriers exist before anyone arrives on them remotely
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wc{dead, p.ctl, p.limit_ns, -1, (int)blockIdx.x};
+  const int n_chunks = (p.ntl + TI - 1) / TI;
+  const int T = p.T;
+
+  // Items of a chunk: for s in [0,T] : for j in [0,TI).  Item (s,j) first (s > 0) forms
+  // dh = d_ifgo[T-s] x Wh for its tile, then (s < T) does the gate maths of step t = T-1-s.
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(w_full, (uint32_t)((size_t)H * 128));
+      for (int kc = 0; kc < KC; ++kc)
+        tma_load_2d(w_s + (size_t)kc * 8192, &tmW, w_full, ugc * 64, (int)r * H + kc * RK);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int ch = 0; ch < n_chunks && ok; ++ch) {
+        for (int st = 1; st <= T && ok; ++st) {
+          const int tg = T - st;      // timestep whose d_ifgo is streamed
+          for (int j = 0; j < TI && ok; ++j) {
+            const int bt = pb + (ch * TI + j) * p.nb_par;
+            if (bt >= p.nbt) continue;
+            wc.d0 = tg; wc.d1 = bt;
+            if (!wait_flag_ge(&p.flags[(size_t)tg * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, tg, bt)) {
+              *dead = 1; ok = false; break;
+            }
+            fence_proxy_async();
+            const int row0 = bt * RB, col0 = (int)r * H;
+            for (int kc = 0; kc < KC; ++kc) {
+              if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
+              mbar_expect_tx(&full[s], R_STAGE_BYTES);
+              tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmG, &full[s], col0 + kc * RK, row0, tg);
+              if (++s == R_STAGES) { s = 0; ph ^= 1; }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp < FIRST_EPI) {
+    // ---------------------------------------------------------------- MMA issuers
+    const int x = warp - 1;
+    if (lane == 0) {
+      constexpr uint64_t descA = smem_desc_base(16, 1024);       // d_ifgo tile, K-major
+      constexpr uint64_t descB = smem_desc_base(8192, 1024);     // Wh chunk, N-major (64 units wide)
+      const uint32_t idesc = instr_desc(p.fmt, 0, 1, RB, N);
+      bool ok = mbar_wait(w_full, 0, wc);
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t acc_ph[2] = {0, 0};
+      int it = 0;
+      const uint32_t w_addr = smem_u32(w_s);
+      for (int ch = 0; ch < n_chunks && ok; ++ch) {
+        for (int st = 1; st <= T && ok; ++st) {
+          for (int j = 0; j < TI && ok; ++j) {
+            const int bt = pb + (ch * TI + j) * p.nb_par;
+            if (bt >= p.nbt) continue;
+            const int a = it & 1;
+            ++it;
+            if (!mbar_wait(&acc_empty[a], acc_ph[a] ^ 1, wc)) { ok = false; break; }
+            acc_ph[a] ^= 1;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + a * ACC_STRIDE + x * N;
+            for (int kc = 0; kc < KC; ++kc) {
+              if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES) + x * 32;
+              const uint32_t sb = w_addr + (uint32_t)kc * 8192 + x * 2048;
+              umma_f16(d_tmem, smem_desc(descA, sa), smem_desc(descB, sb), idesc, kc > 0 ? 1u : 0u);
+              umma_commit(&empty[s]);
+              if (++s == R_STAGES) { s = 0; ph ^= 1; }
+            }
+            if (ok) umma_commit(&acc_full[a]);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue: thread = batch row
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    const int unit0 = ugc * 64 + (int)r * 16;
+    const size_t H4 = 4 * (size_t)H;
+    const T16* ifgo = reinterpret_cast<const T16*>(p.ifgo);
+    const T16* cell = reinterpret_cast<const T16*>(p.cell);
+    const T16* dout = reinterpret_cast<const T16*>(p.dout);
+    T16* dg = reinterpret_cast<T16*>(p.d_ifgo);
+    uint32_t acc_ph[2] = {0, 0};
+    uint32_t x_ph[2] = {0, 0};
+    int it = 0;
+    bool ok = true;
+    // where this CTA's slices land in each peer, and the peers' exchange barriers
+    uint32_t peer_recv[4], peer_bar[4];
+#pragma unroll
+    for (int dst = 0; dst < 4; ++dst) {
+      const int slot = (int)r < dst ? (int)r : (int)r - 1;      // index of this source among dst's 3 senders
+      peer_recv[dst] = mapa_shared(smem_u32(recv) + slot * XSLOT_BYTES + row_in_tile * 64, dst);
+      peer_bar[dst] = mapa_shared(smem_u32(&xchg[0]), dst);
+    }
+    for (int ch = 0; ch < n_chunks && ok; ++ch) {
+      float dc[TI][16], dhc[TI][16];
+      uint4 pf[14];     // next item's inputs: 4 gates (8), c[t+1] (2), c[t] (2), dout[t] (2)
+#pragma unroll
+      for (int j = 0; j < TI; ++j) {
+        const int bt = pb + (ch * TI + j) * p.nb_par;
+        const int row = bt * RB + row_in_tile;
+        const bool rok = bt < p.nbt && row < p.B;
+        if (rok && p.dc_n) {
+          const T16* src = reinterpret_cast<const T16*>(p.dc_n) + (size_t)row * H + unit0;
+          unpack16<T16>(ldg16(src), ldg16(src + 8), dc[j]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 16; ++u) dc[j][u] = 0.f;
+        }
+        if (rok && p.dh_n) {
+          const T16* src = reinterpret_cast<const T16*>(p.dh_n) + (size_t)row * H + unit0;
+          unpack16<T16>(ldg16(src), ldg16(src + 8), dhc[j]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 16; ++u) dhc[j][u] = 0.f;
+        }
+      }
+      auto prefetch = [&](int t, int bt) {
+        const int row = bt * RB + row_in_tile;
+        if (bt < p.nbt && row < p.B) {
+          const T16* g = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { pf[2 * k] = ldg16(g + (size_t)k * H); pf[2 * k + 1] = ldg16(g + (size_t)k * H + 8); }
+          const T16* c1 = cell + ((size_t)(t + 1) * p.B + row) * H + unit0;
+          const T16* c0 = cell + ((size_t)t * p.B + row) * H + unit0;
+          const T16* dd = dout + ((size_t)t * p.B + row) * H + unit0;
+          pf[8] = ldg16(c1); pf[9] = ldg16(c1 + 8);
+          pf[10] = ldg16(c0); pf[11] = ldg16(c0 + 8);
+          pf[12] = ldg16(dd); pf[13] = ldg16(dd + 8);
+        }
+      };
+      prefetch(T - 1, pb + (ch * TI) * p.nb_par);
+      for (int st = 0; st <= T && ok; ++st) {
+#pragma unroll
+        for (int j = 0; j < TI; ++j) {
+          const int bt = pb + (ch * TI + j) * p.nb_par;
+          if (bt >= p.nbt) continue;
+          const int row = bt * RB + row_in_tile;
+          const bool row_ok = row < p.B;
+          if (st > 0) {
+            // ---- dh = (sum over the cluster's four K ranges of) d_ifgo[T-st] x Wh
+            const int a = it & 1;
+            ++it;
+            wc.d0 = T - st; wc.d1 = bt;
+            if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
+            acc_ph[a] ^= 1;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16);
+            float own[16];
+#pragma unroll
+            for (int dst = 0; dst < 4; ++dst) {
+              uint32_t v[16];
+              tmem_ld_32x16(taddr + dst * 16, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int xx = 1; xx < NACC; ++xx) {
+                uint32_t w[16];
+                tmem_ld_32x16(taddr + xx * N + dst * 16, w);
+                tmem_ld_wait();
+#pragma unroll
+                for (int u = 0; u < 16; ++u) v[u] = __float_as_uint(__uint_as_float(v[u]) + __uint_as_float(w[u]));
+              }
+              if (dst == (int)r) {
+#pragma unroll
+                for (int u = 0; u < 16; ++u) own[u] = __uint_as_float(v[u]);
+              } else {
+                const uint32_t ra = peer_recv[dst] + j * (3 * XSLOT_BYTES);
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4)
+                  st_cluster_v4(ra + c4 * 16, __uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1]),
+                                __uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3]));
+              }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(&acc_empty[a]);
+#pragma unroll
+              for (int dst = 0; dst < 4; ++dst)
+                if (dst != (int)r) mbar_arrive_remote(peer_bar[dst] + j * 8);
+            }
+            if (!mbar_wait_cluster(&xchg[j], x_ph[j], wc)) { ok = false; break; }
+            x_ph[j] ^= 1;
+            const float* rv = recv + (size_t)j * (3 * XSLOT_BYTES / 4) + row_in_tile * 16;
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+              dhc[j][u] = own[u] + rv[u] + rv[XSLOT_BYTES / 4 + u] + rv[2 * (XSLOT_BYTES / 4) + u];
+          }
+          if (st < T) {
+            // ---- gate maths of step t for this thread's row and 16 units
+            const int t = T - 1 - st;
+            float pi[16], pf_[16], pg[16], po[16], c1[16], c0[16], dd[16];
+            unpack16<T16>(pf[0], pf[1], pi);
+            unpack16<T16>(pf[2], pf[3], pf_);
+            unpack16<T16>(pf[4], pf[5], pg);
+            unpack16<T16>(pf[6], pf[7], po);
+            unpack16<T16>(pf[8], pf[9], c1);
+            unpack16<T16>(pf[10], pf[11], c0);
+            unpack16<T16>(pf[12], pf[13], dd);
+            float qi[16], qf[16], qg[16], qo[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+              const float si = sigmoid_fast(pi[u]), sf = sigmoid_fast(pf_[u]), so = sigmoid_fast(po[u]);
+              const float tg = tanh_fast(pg[u]), tc = tanh_fast(c1[u]);
+              const float dh = dd[u] + dhc[j][u];
+              const float dcv = fmaf(dh * so, 1.f - tc * tc, dc[j][u]);
+              qi[u] = dcv * tg * si * (1.f - si);
+              qf[u] = dcv * c0[u] * sf * (1.f - sf);
+              qg[u] = dcv * si * (1.f - tg * tg);
+              qo[u] = dh * tc * so * (1.f - so);
+              dc[j][u] = dcv * sf;
+            }
+            if (row_ok) {
+              T16* dst = dg + ((size_t)t * p.B + row) * H4 + unit0;
+              store16<T16>(dst, qi);
+              store16<T16>(dst + (size_t)H, qf);
+              store16<T16>(dst + 2 * (size_t)H, qg);
+              store16<T16>(dst + 3 * (size_t)H, qo);
+            }
+            // publish d_ifgo[t] rows of this warp, then (after the release) fetch the next item's inputs
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)t * p.nbt + bt], 1);
+            {
+              int nj = j + 1, ns = st;
+              if (nj == TI || pb + (ch * TI + nj) * p.nb_par >= p.nbt) { nj = 0; ns = st + 1; }
+              if (ns < T) prefetch(T - 1 - ns, pb + (ch * TI + nj) * p.nb_par);
+            }
+          } else if (row_ok) {
+            // ---- after the last step: the carries are the gradients of the initial state
+            store16<T16>(reinterpret_cast<T16*>(p.dh0) + (size_t)row * H + unit0, dhc[j]);
+            store16<T16>(reinterpret_cast<T16*>(p.dc0) + (size_t)row * H + unit0, dc[j]);
+          }
+        }
+      }
+    }
+  }
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  cluster_sync_all();   // no CTA leaves while a peer may still write into its shared memory
+}
+
+// Column sums of d_ifgo [rows, cols] (16-bit) over DB_PARTS interleaved row groups -> part[DB_PARTS][cols].
+template <typename T16>
+__global__ void __launch_bounds__(128) colsum_kernel(const T16* __restrict__ g, int rows, int cols, float* __restrict__ part) {
+  const int col = blockIdx.x * 128 + threadIdx.x;
+  if (col >= cols) return;
+  float s = 0.f;
+  for (int rr = blockIdx.y; rr < rows; rr += DB_PARTS) s += Elem<T16>::to_f(g[(size_t)rr * cols + col]);
+  part[(size_t)blockIdx.y * cols + col] = s;
+}
+
+template <int TI, typename T16>
+static int launch_bwd_t(const BwdPlan& pl, const CUtensorMap& tw, const CUtensorMap& tg, BwdParams& p, cudaStream_t st) {
+  auto kern = bwd_kernel<TI, T16>;
+  BLSTM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.grid);
+  cfg.blockDim = dim3(pl.threads);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 4;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeCooperative;
+  attrs[1].val.cooperative = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 2;
+  // every CTA spins on its peers: the whole grid has to be resident at once
+  int max_clusters = 0;
+  BLSTM_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg));
+  if (max_clusters * 4 < pl.grid) return BLSTM_E_NOT_CORESIDENT;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tg, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    cfg.numAttrs = 1;   // cooperative + cluster refused: the occupancy check above already proved co-residency
+    e = cudaLaunchKernelEx(&cfg, kern, tw, tg, p);
+  }
+  BLSTM_CUDA_OK(e);
+  count_launch();
+  return BLSTM_OK;
+}
+
 }  // namespace sm100
 
 #ifdef BLSTM_REC_TRACE
@@ -423,8 +853,12 @@ extern "C" int blstm_dbg_rtrace(long long* host, int n) {
 
 using namespace sm100;
 
-bool sm100_recurrence_supported(const blstm_desc& d, int phase) { return make_plan(d, phase).ok; }
-size_t sm100_recurrence_workspace(const blstm_desc& d, int phase) { return make_plan(d, phase).ws_bytes; }
+bool sm100_recurrence_supported(const blstm_desc& d, int phase) {
+  return phase == BLSTM_PHASE_BWD ? make_bwd_plan(d).ok : make_plan(d, phase).ok;
+}
+size_t sm100_recurrence_workspace(const blstm_desc& d, int phase) {
+  return phase == BLSTM_PHASE_BWD ? make_bwd_plan(d).ws_bytes : make_plan(d, phase).ws_bytes;
+}
 
 int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* out, void* cell, void* ws,
                          size_t ws_bytes, cudaStream_t st) {
@@ -475,9 +909,59 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   return BLSTM_E_UNSUPPORTED;
 }
 
-int sm100_bwd_recurrence(const blstm_desc&, const void*, const void*, const void*, const void*, const void*,
-                         const void*, void*, void*, void*, float*, void*, size_t, cudaStream_t) {
-  return BLSTM_E_UNSUPPORTED;
+int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n, const void* dc_n,
+                         const void* ifgo, const void* cell, const void* Wh, void* d_ifgo, void* dh0, void* dc0,
+                         float* db, void* ws, size_t ws_bytes, cudaStream_t st) {
+  const BwdPlan pl = make_bwd_plan(d);
+  if (!pl.ok) return BLSTM_E_UNSUPPORTED;
+  if (ws_bytes < pl.ws_bytes) return BLSTM_E_WORKSPACE;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc) return rc;
+  if (!di.coop || pl.grid > di.sm_count) return BLSTM_E_NOT_CORESIDENT;
+  const int H = d.hidden_size, B = d.batch, T = d.seq_len;
+  CUtensorMap tw, tg;
+  {  // Wh [4H,H] row-major: rows are K (gate-major), columns the output units (N-major operand)
+    uint64_t dims[2] = {(uint64_t)H, (uint64_t)4 * H};
+    uint64_t str[1] = {(uint64_t)H * 2};
+    uint32_t box[2] = {64, 64};
+    rc = encode_tensor_map(&tw, Wh, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  {  // d_ifgo [T,B,4H] as {k, batch row, t}
+    uint64_t dims[3] = {(uint64_t)4 * H, (uint64_t)B, (uint64_t)T};
+    uint64_t str[2] = {(uint64_t)4 * H * 2, (uint64_t)B * 4 * H * 2};
+    uint32_t box[3] = {RK, RB, 1};
+    rc = encode_tensor_map(&tg, d_ifgo, 3, dims, str, box);
+    if (rc) return rc;
+  }
+  BLSTM_CUDA_OK(cudaMemsetAsync(ws, 0, pl.off_db, st));
+  BwdParams p;
+  p.T = T; p.B = B; p.H = H;
+  p.nbt = pl.nbt; p.nug = pl.nug; p.nb_par = pl.nb_par; p.ntl = pl.ntl; p.stages = pl.stages;
+  p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
+  p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
+  p.flag_target = (H / 16) * 4;
+  p.limit_ns = d.wait_limit_us > 0 ? (unsigned long long)d.wait_limit_us * 1000ull : kDefaultWaitNs;
+  p.ctl = reinterpret_cast<Control*>(ws);
+  p.flags = reinterpret_cast<int*>(static_cast<char*>(ws) + pl.off_flags);
+  p.dout = dout; p.dh_n = dh_n; p.dc_n = dc_n; p.ifgo = ifgo; p.cell = cell;
+  p.d_ifgo = d_ifgo; p.dh0 = dh0; p.dc0 = dc0;
+  const bool bf = d.dtype == BLSTM_BF16;
+  if (pl.TI == 1) rc = bf ? launch_bwd_t<1, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<1, __half>(pl, tw, tg, p, st);
+  else            rc = bf ? launch_bwd_t<2, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<2, __half>(pl, tw, tg, p, st);
+  if (rc) return rc;
+  if (db) {
+    float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + pl.off_db);
+    const int rows = T * B, cols = 4 * H;
+    dim3 grid(cdiv(cols, 128), DB_PARTS);
+    if (bf) colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)d_ifgo, rows, cols, part);
+    else    colsum_kernel<__half><<<grid, 128, 0, st>>>((const __half*)d_ifgo, rows, cols, part);
+    BLSTM_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return reduce_db(part, DB_PARTS, cols, db, st);
+  }
+  return BLSTM_OK;
 }
 
 }  // namespace blstm

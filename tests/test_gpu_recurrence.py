@@ -90,3 +90,49 @@ def test_forward_recurrence(dtype, shape):
     # bit-identical when repeated
     ifgo3, out3, _ = _fwd(lib, d, pre, Wh, h0, c0)
     assert torch.equal(out, out3) and torch.equal(ifgo, ifgo3)
+
+
+BWD_SHAPES = [(3, 128, 64), (5, 200, 128), (8, 256, 256), (4, 64, 1024), (6, 1300, 512), (1, 40, 64), (30, 96, 256)]
+
+
+def _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh):
+    T, B, H = d.seq_len, d.batch, d.hidden_size
+    dg = torch.full((T, B, 4 * H), float("nan"), device="cuda", dtype=ifgo.dtype)
+    dh0 = torch.full((B, H), float("nan"), device="cuda", dtype=ifgo.dtype)
+    dc0 = torch.full((B, H), float("nan"), device="cuda", dtype=ifgo.dtype)
+    db = torch.full((4 * H,), float("nan"), device="cuda")
+    n = lib.blstm_workspace_bytes(d, _lib.PHASE_BWD)
+    ws = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.blstm_bwd_recurrence(d, dout.data_ptr(), dh_n.data_ptr(), dc_n.data_ptr(), ifgo.data_ptr(),
+                                        cell.data_ptr(), Wh.data_ptr(), dg.data_ptr(), dh0.data_ptr(),
+                                        dc0.data_ptr(), db.data_ptr(), ws.data_ptr(), n, s), "bwd_recurrence")
+    _lib.check(lib.blstm_read_status(ws.data_ptr(), None, s), "status")
+    return dg, dh0, dc0, db
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("shape", BWD_SHAPES)
+def test_backward_recurrence(dtype, shape):
+    lib = _lib.load()
+    T, B, H = shape
+    dt = TD[dtype]
+    g = torch.Generator(device="cuda").manual_seed(B * 3 + H)
+    ifgo = torch.randn(T, B, 4 * H, generator=g, device="cuda").to(dt)
+    cell = (torch.randn(T + 1, B, H, generator=g, device="cuda") * 0.7).to(dt)
+    dout = torch.randn(T, B, H, generator=g, device="cuda").to(dt)
+    dh_n = torch.randn(B, H, generator=g, device="cuda").to(dt)
+    dc_n = torch.randn(B, H, generator=g, device="cuda").to(dt)
+    Wh = ((torch.rand(4 * H, H, generator=g, device="cuda") * 2 - 1) / H ** 0.5).to(dt)
+    d = _desc(dtype, T, B, H)
+    assert lib.blstm_plan_name(d, 1) == b"sm100"
+    got = _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh)
+    ref = _bwd(lib, _desc(dtype, T, B, H, _lib.FLAG_FORCE_GENERIC), dout, dh_n, dc_n, ifgo, cell, Wh)
+    tol = 6e-3 if dtype == "fp16" else 4e-2
+    scale = float(ref[0].float().abs().max())
+    _cmp("d_ifgo", got[0], ref[0], tol * max(scale, 1.0))
+    _cmp("dh0", got[1][None], ref[1][None], tol * max(float(ref[1].float().abs().max()), 1.0))
+    _cmp("dc0", got[2][None], ref[2][None], tol * max(float(ref[2].float().abs().max()), 1.0))
+    assert torch.allclose(got[3], got[0].float().sum(dim=(0, 1)), rtol=1e-4, atol=1e-3 * T * B ** 0.5)
+    again = _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh)
+    assert torch.equal(got[0], again[0]) and torch.equal(got[1], again[1]) and torch.equal(got[3], again[3])
