@@ -39,7 +39,7 @@ WORKLOADS = {
     "c5": dict(dtype="bf16", L=2, B=4096, T=256, H=512, bwd=True, batch_first=False, h0=0.0, term=False),
 }
 ESIZE = {"fp32": 4, "fp16": 2, "bf16": 2}
-CPU_SAMPLE_BATCH = {"c1": 16, "c2": 64, "c3": 32, "c4": 32, "c5": 64}
+CPU_SAMPLE_BATCH = {"c1": 16, "c2": 64, "c3": 128, "c4": 32, "c5": 1024}
 
 
 def peaks():
@@ -133,8 +133,12 @@ def main():
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seq-len", type=int, default=0,
+                    help="override T (profiling aid: shorter captures; the line then names the override)")
     args = ap.parse_args()
-    wl, cfg = args.workload, WORKLOADS[args.workload]
+    wl, cfg = args.workload, dict(WORKLOADS[args.workload])
+    if args.seq_len > 0:
+        cfg["T"] = args.seq_len
     if args.impl == "reference":
         return run_reference(args, wl, cfg)
     args.warmup = max(args.warmup, 3)
@@ -234,48 +238,77 @@ def main():
     value = tokens / (ms_step * 1e-3)
     e2e_value = tokens / (ms_e2e / args.steps * 1e-3)
 
-    # ---- roofline of the dominant kernel: forward recurrence timed alone (rank-local)
+    # ---- roofline: both persistent recurrence kernels timed alone (rank-local, CUDA events on the
+    # launching stream); the slower one is the dominant kernel of the step and goes in "roofline"
     hbm_gbs, tflops, which = peaks()
     es = ESIZE[cfg["dtype"]]
     d = _lib.Desc(_lib.DTYPE_CODE[cfg["dtype"]], T, B, H, H, 0, 0, 0)
-    nws = lib.blstm_workspace_bytes(d, _lib.PHASE_FWD)
-    ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    Wh = model.weight_hh_l0.detach()
     pre = (torch.randn(T, B, 4 * H, device=dev) * 0.5).to(dt)
     ifgo = torch.empty_like(pre)
-    Wh = model.weight_hh_l0.detach()
     states = torch.zeros(2, T + 1, B, H, device=dev, dtype=dt)
-    st = torch.cuda.current_stream().cuda_stream
-    durs = []
-    for i in range(3 + 5):
-        ifgo.copy_(pre)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        _lib.check(lib.blstm_fwd_recurrence(d, ifgo.data_ptr(), Wh.data_ptr(), states[0].data_ptr(),
-                                            states[1].data_ptr(), ws.data_ptr(), nws, st), "fwd_recurrence")
-        e1.record()
-        torch.cuda.synchronize()
-        if i >= 3:
-            durs.append(e0.elapsed_time(e1))
-    rec_ms = sum(durs) / len(durs)
+    nws = lib.blstm_workspace_bytes(d, _lib.PHASE_FWD)
+    ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+
+    def time_launch(fn, prep=None, n=5, w=3):
+        durs = []
+        for i in range(w + n):
+            if prep:
+                prep()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= w:
+                durs.append(e0.elapsed_time(e1))
+        return sum(durs) / len(durs)
+
+    fwd_ms = time_launch(
+        lambda: _lib.check(lib.blstm_fwd_recurrence(d, ifgo.data_ptr(), Wh.data_ptr(), states[0].data_ptr(),
+                                                    states[1].data_ptr(), ws.data_ptr(), nws, st), "fwd_recurrence"),
+        prep=lambda: ifgo.copy_(pre))
+    kernels = {"forward recurrence": fwd_ms}
+    if cfg["bwd"]:
+        nwb = lib.blstm_workspace_bytes(d, _lib.PHASE_BWD)
+        wsb = torch.empty(nwb, dtype=torch.uint8, device=dev)
+        dg = torch.empty_like(pre)
+        carries = torch.empty(2, B, H, device=dev, dtype=dt)
+        kernels["backward recurrence"] = time_launch(
+            lambda: _lib.check(lib.blstm_bwd_recurrence(d, dout.data_ptr() if not cfg["batch_first"] else pre.data_ptr(),
+                                                        None, None, ifgo.data_ptr(), states[1].data_ptr(), Wh.data_ptr(),
+                                                        dg.data_ptr(), carries[0].data_ptr(), carries[1].data_ptr(), None,
+                                                        wsb.data_ptr(), nwb, st), "bwd_recurrence"))
+        del dg, wsb
     alg_bytes = 10.0 * B * H * es * T + 4.0 * H * H * es       # 10*B*H*e per step + Wh once
     alg_flops = 8.0 * B * H * H * T
     hbm_time = alg_bytes / (hbm_gbs * 1e9)
     tensor_time = alg_flops / (tflops * 1e12)
-    if hbm_time >= tensor_time:
-        roof = {"bound": "hbm", "achieved": alg_bytes / (rec_ms * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s"}
-    else:
-        roof = {"bound": "tensor", "achieved": alg_flops / (rec_ms * 1e-3) / 1e12, "peak": tflops, "unit": "TFLOP/s"}
-    roof["frac"] = roof["achieved"] / roof["peak"]
-    roof.update({"kernel": "forward recurrence (%s)" % lib.blstm_plan_name(d, 0).decode(),
-                 "peak_source": f"of {which}", "ms_per_launch": rec_ms,
-                 "us_per_timestep": rec_ms * 1e3 / T, "traffic": None})
-    try:
-        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-            tr = json.load(f).get(f"{wl}_fwd_recurrence")
-        if tr:
-            roof["traffic"] = tr["bytes_per_launch_full"]
-    except Exception:
-        pass
+
+    def roof_of(name, ms):
+        if hbm_time >= tensor_time:
+            r = {"bound": "hbm", "achieved": alg_bytes / (ms * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s"}
+        else:
+            r = {"bound": "tensor", "achieved": alg_flops / (ms * 1e-3) / 1e12, "peak": tflops, "unit": "TFLOP/s"}
+        r["frac"] = r["achieved"] / r["peak"]
+        phase = 1 if name.startswith("backward") else 0
+        r.update({"kernel": "%s (%s)" % (name, lib.blstm_plan_name(d, phase).decode()),
+                  "peak_source": f"of {which}", "ms_per_launch": ms, "us_per_timestep": ms * 1e3 / T,
+                  "algorithmic_bytes_per_launch": alg_bytes, "algorithmic_flops_per_launch": alg_flops,
+                  "traffic": None})
+        try:
+            with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+                tr = json.load(f).get(f"{wl}:{name}")
+            if tr:   # DRAM bytes of one ncu capture at T = tr["T"], scaled by the timesteps of this launch
+                r["traffic"] = tr["dram_bytes"] * (T / tr["T"]) * (B / tr["B"])
+        except Exception:
+            pass
+        return r
+
+    dominant = max(kernels, key=kernels.get)
+    roof = roof_of(dominant, kernels[dominant])
+    roof_other = {k: roof_of(k, v) for k, v in kernels.items() if k != dominant}
     del pre, ifgo, states, ws
 
     line = {
@@ -283,7 +316,8 @@ def main():
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": cfg["dtype"], "data": "synthetic",
-        "config": {"workload": wl, "L": L, "B": Bg, "B_per_gpu": B, "T": T, "I": H, "H": H,
+        "config": {"workload": wl if not args.seq_len else f"{wl} with T overridden to {T} (profiling run, not the benchmark)",
+                   "L": L, "B": Bg, "B_per_gpu": B, "T": T, "I": H, "H": H,
                    "pass": "fwd+bwd" if cfg["bwd"] else "fwd", "sharding": f"batch/{world}",
                    "collective": "one fp32 sum-allreduce of dWx,dWh,db (NCCL)" if bucket is not None else "none",
                    "l2": "inputs larger than L2 (no flush needed)" if x_host.numel() * es > 126e6 else "inputs smaller than L2; not flushed",
@@ -295,6 +329,7 @@ def main():
         "gpu_launches": launches,
         "clocks": sampler.result(),
         "roofline": roof,
+        "roofline_other_kernels": roof_other,
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

@@ -63,6 +63,15 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t raddr, float a, float b, 
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
+// Bulk asynchronous copy of `bytes` (multiple of 16) from this CTA's shared memory into a peer
+// CTA's shared memory; completion is signalled as transaction bytes on the PEER's mbarrier.
+__device__ __forceinline__ void dsmem_bulk_copy(uint32_t remote_dst, const void* local_src, uint32_t bytes,
+                                                uint32_t remote_bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(remote_dst), "r"(smem_u32(local_src)), "r"(bytes), "r"(remote_bar)
+      : "memory");
+}
 // arrive (release, cluster scope) on an mbarrier that lives in a peer CTA's shared memory
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t remote_bar_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");

@@ -17,6 +17,8 @@
 //   warp 0      TMA producer (flag wait, h tiles, Wh slice once)
 //   warp 1      tcgen05.mma issuer, TMEM owner
 //   warps 2..   epilogue: thread = batch row, 16 hidden units x 4 gates per thread
+#include <stdlib.h>
+
 #include "generic.cuh"
 #include "sm100.cuh"
 #include "sm100_common.cuh"
@@ -429,7 +431,8 @@ static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensor
 // published with the same per-(step, batch tile) arrival counters as the forward kernel).
 // =====================================================================================
 constexpr int DB_PARTS = 64;              // row groups of the bias-gradient column sum
-constexpr int XSLOT_BYTES = RB * 16 * 4;  // one received slice: 128 rows x 16 fp32
+constexpr int XROW_BYTES = 64;            // one row of a slice: 16 fp32; its four 16-byte pieces are XOR-swizzled
+constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x 16 fp32 = 8 KB
 
 struct BwdPlan {
   bool ok;
@@ -456,7 +459,11 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.grid = p.nb_par * per_tile;
   p.threads = 32 * (1 + 4 + 4);
   p.w_bytes = (size_t)H * 128;
-  p.recv_bytes = (size_t)p.TI * 3 * XSLOT_BYTES;
+  p.recv_bytes = (size_t)p.TI * 2 * 3 * XSLOT_BYTES;       // receive slots + send staging
+  if (1024 + p.w_bytes + p.recv_bytes + 256 + 3 * R_STAGE_BYTES > 232448 && p.TI == 2) {
+    p.TI = 1;                                               // not enough room to interleave two tiles
+    p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
+  }
   const size_t fixed = 1024 + p.w_bytes + p.recv_bytes + 256;
   if (fixed + 2 * R_STAGE_BYTES > 232448) return p;
   p.stages = (int)((232448 - fixed) / R_STAGE_BYTES);
@@ -516,8 +523,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   const int KC = H / RK;
   const int R_STAGES = p.stages;
   uint8_t* w_s = smem;                                        // [KC][64 k rows][128 B]
-  float* recv = reinterpret_cast<float*>(smem + (size_t)H * 128);   // [TI][3][128][16]
-  uint8_t* a_s = reinterpret_cast<uint8_t*>(recv) + (size_t)TI * 3 * XSLOT_BYTES;
+  uint8_t* recv = smem + (size_t)H * 128;                     // [TI][3 senders][128 rows][64 B]
+  uint8_t* stage = recv + (size_t)TI * 3 * XSLOT_BYTES;      // [TI][3 receivers][128 rows][64 B]
+  uint8_t* a_s = stage + (size_t)TI * 3 * XSLOT_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * R_STAGE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + R_MAX_STAGES;
@@ -525,7 +533,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint64_t* acc_empty = acc_full + 2;
   uint64_t* w_full = acc_empty + 2;
   uint64_t* xchg = w_full + 1;                                // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xchg + 2);
+  uint64_t* staged = xchg + 2;                                // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(staged + 2);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -538,7 +547,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NACC); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], NACC); mbar_init(&acc_empty[a], EW); }
     mbar_init(w_full, 1);
-    for (int j = 0; j < 2; ++j) mbar_init(&xchg[j], 3 * EW);
+    for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], EW); }   // xchg: one expect_tx arrival + tx bytes
     *dead = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmW);
@@ -575,6 +584,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (!wait_flag_ge(&p.flags[(size_t)tg * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, tg, bt)) {
               *dead = 1; ok = false; break;
             }
+            if (j == 0) RTRACE(st * 8 + 0, (long long)clock64());
             fence_proxy_async();
             const int row0 = bt * RB, col0 = (int)r * H;
             for (int kc = 0; kc < KC; ++kc) {
@@ -613,6 +623,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             const uint32_t d_tmem = tmem_base + a * ACC_STRIDE + x * N;
             for (int kc = 0; kc < KC; ++kc) {
               if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
+              if (kc == 0 && j == 0 && x == 0) RTRACE(st * 8 + 1, (long long)clock64());
               tc_fence_after();
               const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES) + x * 32;
               const uint32_t sb = w_addr + (uint32_t)kc * 8192 + x * 2048;
@@ -621,6 +632,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               if (++s == R_STAGES) { s = 0; ph ^= 1; }
             }
             if (ok) umma_commit(&acc_full[a]);
+            if (j == 0 && x == 0) RTRACE(st * 8 + 2, (long long)clock64());
           }
         }
       }
@@ -630,13 +642,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
     const int unit0 = ugc * 64 + (int)r * 16;
+    const int swz = (row_in_tile >> 1) & 3;   // bank swizzle of the exchanged slices
     const size_t H4 = 4 * (size_t)H;
     const T16* ifgo = reinterpret_cast<const T16*>(p.ifgo);
     const T16* cell = reinterpret_cast<const T16*>(p.cell);
     const T16* dout = reinterpret_cast<const T16*>(p.dout);
     T16* dg = reinterpret_cast<T16*>(p.d_ifgo);
     uint32_t acc_ph[2] = {0, 0};
-    uint32_t x_ph[2] = {0, 0};
+    uint32_t x_ph[2] = {0, 0}, s_ph[2] = {0, 0};
     int it = 0;
     bool ok = true;
     // where this CTA's slices land in each peer, and the peers' exchange barriers
@@ -644,7 +657,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 #pragma unroll
     for (int dst = 0; dst < 4; ++dst) {
       const int slot = (int)r < dst ? (int)r : (int)r - 1;      // index of this source among dst's 3 senders
-      peer_recv[dst] = mapa_shared(smem_u32(recv) + slot * XSLOT_BYTES + row_in_tile * 64, dst);
+      peer_recv[dst] = mapa_shared(smem_u32(recv) + slot * XSLOT_BYTES, dst);
       peer_bar[dst] = mapa_shared(smem_u32(&xchg[0]), dst);
     }
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
@@ -699,47 +712,67 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             wc.d0 = T - st; wc.d1 = bt;
             if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
             acc_ph[a] ^= 1;
+            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 3, (long long)clock64());
             tc_fence_after();
             const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16);
             float own[16];
 #pragma unroll
             for (int dst = 0; dst < 4; ++dst) {
-              uint32_t v[16];
-              tmem_ld_32x16(taddr + dst * 16, v);
+              // the four issuers' partial accumulators for these 16 units: four loads, ONE wait
+              uint32_t v[NACC][16];
+#pragma unroll
+              for (int xx = 0; xx < NACC; ++xx) tmem_ld_32x16(taddr + xx * N + dst * 16, v[xx]);
               tmem_ld_wait();
+              float sum[16];
 #pragma unroll
-              for (int xx = 1; xx < NACC; ++xx) {
-                uint32_t w[16];
-                tmem_ld_32x16(taddr + xx * N + dst * 16, w);
-                tmem_ld_wait();
-#pragma unroll
-                for (int u = 0; u < 16; ++u) v[u] = __float_as_uint(__uint_as_float(v[u]) + __uint_as_float(w[u]));
-              }
+              for (int u = 0; u < 16; ++u)
+                sum[u] = (__uint_as_float(v[0][u]) + __uint_as_float(v[1][u])) +
+                         (__uint_as_float(v[2][u]) + __uint_as_float(v[3][u]));
               if (dst == (int)r) {
 #pragma unroll
-                for (int u = 0; u < 16; ++u) own[u] = __uint_as_float(v[u]);
+                for (int u = 0; u < 16; ++u) own[u] = sum[u];
               } else {
-                const uint32_t ra = peer_recv[dst] + j * (3 * XSLOT_BYTES);
+                // stage the slice for peer `dst` locally (row = 64 B, 16-byte pieces XOR-swizzled)
+                uint8_t* sp = stage + ((size_t)j * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES +
+                              row_in_tile * XROW_BYTES;
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4)
-                  st_cluster_v4(ra + c4 * 16, __uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1]),
-                                __uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3]));
+                  *reinterpret_cast<float4*>(sp + ((c4 ^ swz) << 4)) =
+                      make_float4(sum[4 * c4], sum[4 * c4 + 1], sum[4 * c4 + 2], sum[4 * c4 + 3]);
               }
             }
             tc_fence_before();
+            fence_proxy_async_smem();                 // staged slices -> visible to the bulk-copy engine
             __syncwarp();
-            if (lane == 0) {
-              mbar_arrive(&acc_empty[a]);
+            if (lane == 0) { mbar_arrive(&acc_empty[a]); mbar_arrive(&staged[j]); }
+            // one thread ships the three slices once all four epilogue warps have staged theirs
+            // (bounded mbarrier wait, never a named barrier: a warp that gave up must not strand the rest)
+            if (warp == FIRST_EPI && lane == 0 && mbar_wait(&staged[j], s_ph[j], wc)) {
+              mbar_expect_tx(&xchg[j], 3 * XSLOT_BYTES);      // what this CTA is about to receive
 #pragma unroll
               for (int dst = 0; dst < 4; ++dst)
-                if (dst != (int)r) mbar_arrive_remote(peer_bar[dst] + j * 8);
+                if (dst != (int)r)
+                  dsmem_bulk_copy(peer_recv[dst] + j * (3 * XSLOT_BYTES),
+                                  stage + ((size_t)j * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES,
+                                  XSLOT_BYTES, peer_bar[dst] + j * 8);
             }
+            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 4, (long long)clock64());
+            s_ph[j] ^= 1;
             if (!mbar_wait_cluster(&xchg[j], x_ph[j], wc)) { ok = false; break; }
             x_ph[j] ^= 1;
-            const float* rv = recv + (size_t)j * (3 * XSLOT_BYTES / 4) + row_in_tile * 16;
+            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 5, (long long)clock64());
+            const uint8_t* rv = recv + (size_t)j * (3 * XSLOT_BYTES) + row_in_tile * XROW_BYTES;
 #pragma unroll
-            for (int u = 0; u < 16; ++u)
-              dhc[j][u] = own[u] + rv[u] + rv[XSLOT_BYTES / 4 + u] + rv[2 * (XSLOT_BYTES / 4) + u];
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const int off = (c4 ^ swz) << 4;
+              const float4 s0 = *reinterpret_cast<const float4*>(rv + off);
+              const float4 s1 = *reinterpret_cast<const float4*>(rv + XSLOT_BYTES + off);
+              const float4 s2 = *reinterpret_cast<const float4*>(rv + 2 * XSLOT_BYTES + off);
+              dhc[j][4 * c4 + 0] = own[4 * c4 + 0] + s0.x + s1.x + s2.x;
+              dhc[j][4 * c4 + 1] = own[4 * c4 + 1] + s0.y + s1.y + s2.y;
+              dhc[j][4 * c4 + 2] = own[4 * c4 + 2] + s0.z + s1.z + s2.z;
+              dhc[j][4 * c4 + 3] = own[4 * c4 + 3] + s0.w + s1.w + s2.w;
+            }
           }
           if (st < T) {
             // ---- gate maths of step t for this thread's row and 16 units
@@ -773,9 +806,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               store16<T16>(dst + 3 * (size_t)H, qo);
             }
             // publish d_ifgo[t] rows of this warp, then (after the release) fetch the next item's inputs
+            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 6, (long long)clock64());
             fence_proxy_async();
             __syncwarp();
             if (lane == 0 && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)t * p.nbt + bt], 1);
+            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 7, (long long)clock64());
             {
               int nj = j + 1, ns = st;
               if (nj == TI || pb + (ch * TI + nj) * p.nb_par >= p.nbt) { nj = 0; ns = st + 1; }
@@ -827,7 +862,10 @@ static int launch_bwd_t(const BwdPlan& pl, const CUtensorMap& tw, const CUtensor
   attrs[1].id = cudaLaunchAttributeCooperative;
   attrs[1].val.cooperative = 1;
   cfg.attrs = attrs;
-  cfg.numAttrs = 2;
+  // FASTLSTM_B200_NO_COOP=1 drops the cooperative attribute (profilers that replay kernels refuse
+  // a cooperative cluster launch); co-residency then rests on the occupancy check below alone.
+  static const bool no_coop = [] { const char* e = getenv("FASTLSTM_B200_NO_COOP"); return e && e[0] == '1'; }();
+  cfg.numAttrs = no_coop ? 1 : 2;
   // every CTA spins on its peers: the whole grid has to be resident at once
   int max_clusters = 0;
   BLSTM_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg));
