@@ -47,6 +47,9 @@ SIGNATURES = {
     "blstm_bwd": (c_int, [DP] + [P] * 17 + [c_size_t, P]),
     "blstm_read_status": (c_int, [P, POINTER(c_int32), P]),
     "blstm_launch_count": (ctypes.c_ulonglong, []),
+    "blstm_fwd_recurrence_static": (c_int, [DP, P, P, P, P, P]),
+    "blstm_static_scratch_capacity": (c_size_t, []),
+    "blstm_static_scratch_status": (c_int, [POINTER(c_int32), P]),
 }
 
 _lib = None

@@ -151,6 +151,25 @@ int blstm_bwd(const blstm_desc* d, const void* dout, const void* dh_n, const voi
  * (fastlstm/kernels.py:546-548,1358-1359). */
 int blstm_read_status(const void* workspace, int32_t* detail, void* stream);
 
+/* Forward recurrence WITHOUT a caller-provided workspace.  It has no counterpart in the
+ * reference.  Same contract as blstm_fwd_recurrence (ifgo in/out, out[0]/cell[0] preset,
+ * out[1..T]/cell[1..T] written), but the kernel's scratch - control block and arrival
+ * counters - is a fixed 1 MiB array inside the library's device image, so the call performs
+ * no device allocation of any kind.  It is meant for callers that cannot allocate: a server
+ * whose own arena already owns all free HBM, or a plug-in whose host forbids cudaMalloc once
+ * it is initialised.
+ *   - Limit: blstm_workspace_bytes(d, BLSTM_PHASE_FWD) must be <= blstm_static_scratch_capacity()
+ *     (1 MiB: e.g. T = 1024 with up to 255 batch tiles); larger problems return BLSTM_E_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address (the device must be
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array: two calls that overlap on the GPU (different
+ *     streams, or a second process-wide caller) race on it.  Serialise them.
+ *   - Device-side status of the last call: blstm_static_scratch_status (waits for `stream`). */
+int blstm_fwd_recurrence_static(const blstm_desc* d, void* ifgo, const void* Wh, void* out,
+                                void* cell, void* stream);
+size_t blstm_static_scratch_capacity(void);
+int blstm_static_scratch_status(int32_t* detail, void* stream);
+
 /* Number of kernels this library has launched in this process so far (HOST
  * counter; memsets and copies are not counted).  Benchmarks report the
  * difference across their timed region.  No reference counterpart. */
