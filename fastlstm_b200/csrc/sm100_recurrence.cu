@@ -115,6 +115,7 @@ template <> __device__ __forceinline__ uint32_t pk2<__nv_bfloat16>(float a, floa
 }
 
 __device__ __forceinline__ uint4 ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void stg16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 
 // UH: hidden units per CTA (16 or 32).  TI: batch tiles interleaved per CTA (1 or 2).
@@ -150,11 +151,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   constexpr uint32_t TMEM_COLS = 512;
 
   if (threadIdx.x == 0) {
+    // full[s] is armed (arrive + expected bytes) for its first use here and re-armed by MMA issuer 0
+    // for every later use, which keeps that work out of the latency-bound TMA producer loop
     for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NACC); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], NACC); mbar_init(&acc_empty[a], EW); }
     mbar_init(w_full, 1);
     *dead = 0;
     fence_mbar_init();
+    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], R_STAGE_BYTES);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmH);
   }
@@ -196,7 +200,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             const int row0 = bt * RB;
             for (int kc = 0; kc < KC; ++kc) {
               if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
-              mbar_expect_tx(&full[s], R_STAGE_BYTES);
               tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmH, &full[s], kc * RK, row0, t);
               if (++s == R_STAGES) { s = 0; ph ^= 1; }
             }
@@ -230,6 +233,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             for (int kk = 0; kk < KC; ++kk) {
               const int kc = kk;
               if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
+              if (x == 0) mbar_expect_tx(&full[s], R_STAGE_BYTES);   // arm the stage's next use
               if (kk == 0) RTRACE(t * 8 + 2, (long long)clock64());
               if (t == 100) RTRACE(8192 + kk * 2, (long long)clock64());
               tc_fence_after();
@@ -373,6 +377,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               const T16* src = ifgo + ((size_t)nt * p.B + nrow) * H4 + unit0;
 #pragma unroll
               for (int g = 0; g < 4; ++g) { pre[2 * g] = ldg16(src + (size_t)g * H); pre[2 * g + 1] = ldg16(src + (size_t)g * H + 8); }
+            }
+            // the item after that: only pull its lines into L2
+            int fj = nj + 1, ft = nt;
+            if (fj == TI || pb + (ch * TI + fj) * p.nb_par >= p.nbt) { fj = 0; ft = nt + 1; }
+            const int frow = (pb + (ch * TI + fj) * p.nb_par) * RB + row_in_tile;
+            if (ft < p.T && frow < p.B) {
+              const T16* src = ifgo + ((size_t)ft * p.B + frow) * H4 + unit0;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) prefetch_l2(src + (size_t)g * H);
             }
           }
           // off the critical path: final pre-activations and c[t+1], saved for backward
@@ -544,12 +557,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   constexpr uint32_t TMEM_COLS = 512;
 
   if (threadIdx.x == 0) {
+    // full[s] is armed (arrive + expected bytes) for its first use here and re-armed by MMA issuer 0
+    // for every later use, which keeps that work out of the latency-bound TMA producer loop
     for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NACC); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], NACC); mbar_init(&acc_empty[a], EW); }
     mbar_init(w_full, 1);
     for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], EW); }   // xchg: one expect_tx arrival + tx bytes
     *dead = 0;
     fence_mbar_init();
+    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], R_STAGE_BYTES);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmG);
   }
@@ -589,7 +605,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             const int row0 = bt * RB, col0 = (int)r * H;
             for (int kc = 0; kc < KC; ++kc) {
               if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
-              mbar_expect_tx(&full[s], R_STAGE_BYTES);
               tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmG, &full[s], col0 + kc * RK, row0, tg);
               if (++s == R_STAGES) { s = 0; ph ^= 1; }
             }
@@ -623,6 +638,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             const uint32_t d_tmem = tmem_base + a * ACC_STRIDE + x * N;
             for (int kc = 0; kc < KC; ++kc) {
               if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
+              if (x == 0) mbar_expect_tx(&full[s], R_STAGE_BYTES);   // arm the stage's next use
               if (kc == 0 && j == 0 && x == 0) RTRACE(st * 8 + 1, (long long)clock64());
               tc_fence_after();
               const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES) + x * 32;
@@ -695,6 +711,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           pf[8] = ldg16(c1); pf[9] = ldg16(c1 + 8);
           pf[10] = ldg16(c0); pf[11] = ldg16(c0 + 8);
           pf[12] = ldg16(dd); pf[13] = ldg16(dd + 8);
+        }
+      };
+      // two items ahead the same inputs are only pulled into L2 (no registers to hold them yet)
+      auto prefetch_far = [&](int t, int bt) {
+        const int row = bt * RB + row_in_tile;
+        if (bt < p.nbt && row < p.B) {
+          const T16* g = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) prefetch_l2(g + (size_t)k * H);
+          prefetch_l2(cell + ((size_t)t * p.B + row) * H + unit0);
+          prefetch_l2(dout + ((size_t)t * p.B + row) * H + unit0);
         }
       };
       prefetch(T - 1, pb + (ch * TI) * p.nb_par);
@@ -815,6 +842,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               int nj = j + 1, ns = st;
               if (nj == TI || pb + (ch * TI + nj) * p.nb_par >= p.nbt) { nj = 0; ns = st + 1; }
               if (ns < T) prefetch(T - 1 - ns, pb + (ch * TI + nj) * p.nb_par);
+              int fj = nj + 1, fs = ns;
+              if (fj == TI || pb + (ch * TI + fj) * p.nb_par >= p.nbt) { fj = 0; fs = ns + 1; }
+              if (fs < T) prefetch_far(T - 1 - fs, pb + (ch * TI + fj) * p.nb_par);
             }
           } else if (row_ok) {
             // ---- after the last step: the carries are the gradients of the initial state
