@@ -94,6 +94,19 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Non-blocking probe (mbarrier.test_wait never suspends the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // State every role of a CTA shares for giving up: `dead` lives in shared memory.
 struct WaitCtx {
   volatile int* dead;             // shared-memory flag, set once any wait of this CTA gave up
@@ -154,6 +167,14 @@ static __device__ __noinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t pa
 // Fast path inline (single-thread producer / issuer loops are instruction-latency bound).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
   if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, w);
+}
+// Same, but spins on the non-blocking probe for a while first: lowest wake-up latency for the
+// single-thread MMA-issue loops.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, w);
 }
 

@@ -38,9 +38,36 @@ __device__ long long g_rtrace[16384];
 #define RTRACE(i, v) do { } while (0)
 #endif
 
+// Ring depth R and number of concurrent TMA-issuing lanes / MMA-issuing warps NI.  Every stage
+// barrier must always be waited on by the SAME thread of each role (a parity wait cannot tell
+// phase n from phase n+2, so two threads sharing a barrier could lap each other): stage s belongs
+// to lane / issuer s % NI, which needs NI | R.  NI is also capped by the TMEM accumulators
+// available (max_ni) and by the chunks per item (an issuer without work would leave a stale
+// accumulator).
+static bool pick_ring(size_t fixed_bytes, int max_ni, int kc, int* stages, int* ni) {
+  // Prefer many concurrent issuers, but only count them fully when the ring holds two rounds of
+  // their chunks (R >= 2 NI): with R == NI the loads of one round cannot overlap the MMAs of the
+  // previous one.
+  const int cand[5] = {8, 6, 4, 3, 2};
+  int best_r = 0, best_n = 0, best_score = -1;
+  for (int i = 0; i < 5; ++i) {
+    const int r = cand[i];
+    if (fixed_bytes + (size_t)r * R_STAGE_BYTES > 232448) continue;
+    for (int n = 4; n >= 1; --n) {
+      if (n > max_ni || n > kc || r % n != 0) continue;
+      const int score = (r >= 2 * n) ? 2 * n : n;
+      if (score > best_score) { best_score = score; best_r = r; best_n = n; }
+    }
+  }
+  if (!best_r) return false;
+  *stages = best_r;
+  *ni = best_n;
+  return true;
+}
+
 struct RecPlan {
   bool ok;
-  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages;
+  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages, ni;
   size_t w_bytes, smem;
   size_t off_flags, n_flags, ws_bytes;
 };
@@ -71,9 +98,7 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.threads = 32 * (1 + 256 / p.N + p.epi_warps);   // producer + MMA issuers + epilogue
   p.w_bytes = (size_t)p.N * H * 2;
   const size_t fixed = 1024 + p.w_bytes + 256;
-  if (fixed + 2 * R_STAGE_BYTES > 232448) return p;
-  p.stages = (int)((232448 - fixed) / R_STAGE_BYTES);
-  if (p.stages > R_MAX_STAGES) p.stages = R_MAX_STAGES;
+  if (!pick_ring(fixed, 256 / p.N, H / RK, &p.stages, &p.ni)) return p;
   p.smem = fixed + (size_t)p.stages * R_STAGE_BYTES;
   p.n_flags = (size_t)(d.seq_len + 1) * p.nbt;
   p.off_flags = sizeof(Control);
@@ -86,6 +111,7 @@ struct FwdParams {
   int T, B, H;
   int nbt, nh, nb_par, ntl;
   int stages;
+  int ni;                   // TMA-issuing lanes = MMA-issuing warps in use
   int fmt;
   int no_arrive;
   int flag_target;          // nh * epilogue warps
@@ -149,12 +175,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   constexpr int FIRST_EPI = 1 + NACC;               // first epilogue warp
   constexpr int ACC_STRIDE = NACC * N;              // columns per item buffer (256)
   constexpr uint32_t TMEM_COLS = 512;
+  const int nacc = p.ni;                             // accumulators / issuers / TMA lanes in use
 
   if (threadIdx.x == 0) {
-    // full[s] is armed (arrive + expected bytes) for its first use here and re-armed by MMA issuer 0
-    // for every later use, which keeps that work out of the latency-bound TMA producer loop
-    for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NACC); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], NACC); mbar_init(&acc_empty[a], EW); }
+    // full[s] is armed (arrive + expected bytes) for its first use here and re-armed by the MMA issuer
+    // that consumed it for every later use, which keeps that work out of the latency-bound TMA producer loop
+    for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], nacc); mbar_init(&acc_empty[a], EW); }
     mbar_init(w_full, 1);
     *dead = 0;
     fence_mbar_init();
@@ -175,35 +202,49 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
+    // One thread needs a few hundred clocks per cp.async.bulk.tensor issue, so p.ni lanes issue in
+    // lockstep, each owning the ring stages congruent to its lane index.
     if (lane == 0) {
       // resident Wh slice: rows (gate g, unit ht*UH + u), all K, as KC chunks of [N][64]
       mbar_expect_tx(w_full, (uint32_t)((size_t)N * H * 2));
       for (int kc = 0; kc < KC; ++kc) tma_load_3d(w_s + (size_t)kc * N * 128, &tmW, w_full, kc * RK, ht * UH, 0);
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int ch = 0; ch < n_chunks && ok; ++ch) {
-        for (int t = 0; t < p.T && ok; ++t) {
-          for (int j = 0; j < TI && ok; ++j) {
-            const int bt = pb + (ch * TI + j) * p.nb_par;
-            if (bt >= p.nbt) continue;
-            if (t > 0) {   // h[t] of this batch tile complete: every epilogue warp of every hidden tile arrived
+    }
+    int gs = 0;                // ring position of the current item's chunk 0
+    uint32_t gph = 0;
+    bool ok = true;
+    for (int ch = 0; ch < n_chunks && ok; ++ch) {
+      for (int t = 0; t < p.T && ok; ++t) {
+        for (int j = 0; j < TI && ok; ++j) {
+          const int bt = pb + (ch * TI + j) * p.nb_par;
+          if (bt >= p.nbt) continue;
+          if (t > 0) {   // h[t] of this batch tile complete: every epilogue warp of every hidden tile arrived
+            int seen = 1;
+            if (lane == 0) {
               wc.d0 = t; wc.d1 = bt;
-              if (!wait_flag_ge(&p.flags[(size_t)t * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, t, bt)) {
-                *dead = 1; ok = false; break;
-              }
+              seen = wait_flag_ge(&p.flags[(size_t)t * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, t, bt) ? 1 : 0;
               RTRACE(t * 8 + 0, (long long)clock64());
-              fence_proxy_async();   // peers' generic-proxy stores -> this thread's async-proxy (TMA) reads
-              RTRACE(t * 8 + 1, (long long)clock64());
             }
-            // single-thread loop: kept free of divisions and calls (issue latency is the limit)
-            const int row0 = bt * RB;
-            for (int kc = 0; kc < KC; ++kc) {
-              if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (!seen) { *dead = 1; ok = false; break; }
+            fence_proxy_async();   // peers' generic-proxy stores -> this lane's async-proxy (TMA) reads
+            if (lane == 0) RTRACE(t * 8 + 1, (long long)clock64());
+          }
+          const int row0 = bt * RB;
+          bool lane_ok = true;
+          if (lane < nacc) {
+            // this lane owns ring stages == lane (mod nacc): the item's chunks that land there
+            for (int kc = (lane + nacc - gs % nacc) % nacc; kc < KC; kc += nacc) {
+              int s = gs + kc;
+              uint32_t ph = gph;
+              while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
+              if (!mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
               tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmH, &full[s], kc * RK, row0, t);
-              if (++s == R_STAGES) { s = 0; ph ^= 1; }
+              if (t == 100) RTRACE(8192 + 64 + kc, (long long)clock64());
             }
           }
+          if (__any_sync(0xffffffffu, !lane_ok)) { ok = false; break; }
+          gs += KC;
+          while (gs >= R_STAGES) { gs -= R_STAGES; gph ^= 1; }
         }
       }
     }
@@ -213,9 +254,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     if (lane == 0) {
       constexpr uint64_t descK = smem_desc_base(16, 1024);
       const uint32_t idesc = instr_desc(p.fmt, 0, 0, RB, N);
-      bool ok = mbar_wait(w_full, 0, wc);
-      int s = 0;
-      uint32_t ph = 0;
+      // Every tcgen05 instruction (mma or commit) costs this thread ~150 clocks of issue time, so
+      // issuer x owns WHOLE chunks (kc = x, x+NACC, ...): four MMAs and one commit per chunk,
+      // in parallel with the other issuers, each into its own accumulator.
+      bool ok = (x < nacc) && mbar_wait(w_full, 0, wc);
+      int gs = 0;
+      uint32_t gph = 0;
       uint32_t acc_ph[2] = {0, 0};
       int it = 0;
       const uint32_t w_addr = smem_u32(w_s);
@@ -229,26 +273,31 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (!mbar_wait(&acc_empty[a], acc_ph[a] ^ 1, wc)) { ok = false; break; }
             acc_ph[a] ^= 1;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + a * ACC_STRIDE;
-            for (int kk = 0; kk < KC; ++kk) {
-              const int kc = kk;
-              if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
-              if (x == 0) mbar_expect_tx(&full[s], R_STAGE_BYTES);   // arm the stage's next use
-              if (kk == 0) RTRACE(t * 8 + 2, (long long)clock64());
-              if (t == 100) RTRACE(8192 + kk * 2, (long long)clock64());
+            const uint32_t d_tmem = tmem_base + a * ACC_STRIDE + x * N;
+            uint32_t acc_on = 0;   // first MMA of the item overwrites this issuer's accumulator
+            for (int kc = (x + nacc - gs % nacc) % nacc; kc < KC; kc += nacc) {
+              int s = gs + kc;
+              uint32_t ph = gph;
+              while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
+              if (!mbar_wait_spin(&full[s], ph, wc)) { ok = false; break; }
+              mbar_expect_tx(&full[s], R_STAGE_BYTES);   // arm the stage's next use
+              if (kc == 0) RTRACE(t * 8 + 2, (long long)clock64());
+              if (t == 100) RTRACE(8192 + kc * 2, (long long)clock64());
               tc_fence_after();
               const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES);
               const uint32_t sb = w_addr + (uint32_t)kc * N * 128;
 #pragma unroll
-              for (int k = x; k < RK / 16; k += NACC)
-                umma_f16(d_tmem + x * N, smem_desc(descK, sa + k * 32), smem_desc(descK, sb + k * 32), idesc,
-                         (kk > 0 || k >= NACC) ? 1u : 0u);
+              for (int k = 0; k < RK / 16; ++k)
+                umma_f16(d_tmem, smem_desc(descK, sa + k * 32), smem_desc(descK, sb + k * 32), idesc,
+                         (k > 0) ? 1u : acc_on);
+              acc_on = 1;
               umma_commit(&empty[s]);
-              if (t == 100) RTRACE(8192 + kk * 2 + 1, (long long)clock64());
-              if (++s == R_STAGES) { s = 0; ph ^= 1; }
+              if (t == 100) RTRACE(8192 + kc * 2 + 1, (long long)clock64());
             }
             if (ok) umma_commit(&acc_full[a]);
-            RTRACE(t * 8 + 3, (long long)clock64());
+            if (x == 0) RTRACE(t * 8 + 3, (long long)clock64());
+            gs += KC;
+            while (gs >= R_STAGES) { gs -= R_STAGES; gph ^= 1; }
           }
         }
       }
@@ -316,6 +365,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           tmem_ld_wait();
 #pragma unroll
           for (int x = 1; x < NACC; ++x) {
+            if (x >= nacc) break;
             uint32_t part[4][16];
 #pragma unroll
             for (int g = 0; g < 4; ++g) tmem_ld_32x16(taddr + x * N + g * UH, part[g]);
@@ -449,7 +499,7 @@ constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x
 
 struct BwdPlan {
   bool ok;
-  int nug, nbt, nb_par, ntl, TI, grid, threads, stages;
+  int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni;
   size_t w_bytes, recv_bytes, smem;
   size_t off_flags, n_flags, off_db, ws_bytes;
 };
@@ -478,9 +528,7 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
     p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
   }
   const size_t fixed = 1024 + p.w_bytes + p.recv_bytes + 256;
-  if (fixed + 2 * R_STAGE_BYTES > 232448) return p;
-  p.stages = (int)((232448 - fixed) / R_STAGE_BYTES);
-  if (p.stages > R_MAX_STAGES) p.stages = R_MAX_STAGES;
+  if (!pick_ring(fixed, 4, H / RK, &p.stages, &p.ni)) return p;
   p.smem = fixed + (size_t)p.stages * R_STAGE_BYTES;
   p.n_flags = (size_t)d.seq_len * p.nbt;
   p.off_flags = sizeof(Control);
@@ -494,6 +542,7 @@ struct BwdParams {
   int T, B, H;
   int nbt, nug, nb_par, ntl;
   int stages;
+  int ni;
   int fmt;
   int no_arrive;
   int flag_target;          // (H/16) CTAs per batch tile x 4 epilogue warps
@@ -555,12 +604,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   const int cid = blockIdx.x >> 2;
   const int ugc = cid % p.nug, pb = cid / p.nug;
   constexpr uint32_t TMEM_COLS = 512;
+  const int nacc = p.ni;                             // accumulators / issuers / TMA lanes in use
 
   if (threadIdx.x == 0) {
-    // full[s] is armed (arrive + expected bytes) for its first use here and re-armed by MMA issuer 0
-    // for every later use, which keeps that work out of the latency-bound TMA producer loop
-    for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NACC); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], NACC); mbar_init(&acc_empty[a], EW); }
+    // full[s] is armed (arrive + expected bytes) for its first use here and re-armed by the MMA issuer
+    // that consumed it for every later use, which keeps that work out of the latency-bound TMA producer loop
+    for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], nacc); mbar_init(&acc_empty[a], EW); }
     mbar_init(w_full, 1);
     for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], EW); }   // xchg: one expect_tx arrival + tx bytes
     *dead = 0;
@@ -587,41 +637,53 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       mbar_expect_tx(w_full, (uint32_t)((size_t)H * 128));
       for (int kc = 0; kc < KC; ++kc)
         tma_load_2d(w_s + (size_t)kc * 8192, &tmW, w_full, ugc * 64, (int)r * H + kc * RK);
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int ch = 0; ch < n_chunks && ok; ++ch) {
-        for (int st = 1; st <= T && ok; ++st) {
-          const int tg = T - st;      // timestep whose d_ifgo is streamed
-          for (int j = 0; j < TI && ok; ++j) {
-            const int bt = pb + (ch * TI + j) * p.nb_par;
-            if (bt >= p.nbt) continue;
+    }
+    int gs = 0;
+    uint32_t gph = 0;
+    bool ok = true;
+    for (int ch = 0; ch < n_chunks && ok; ++ch) {
+      for (int st = 1; st <= T && ok; ++st) {
+        const int tg = T - st;      // timestep whose d_ifgo is streamed
+        for (int j = 0; j < TI && ok; ++j) {
+          const int bt = pb + (ch * TI + j) * p.nb_par;
+          if (bt >= p.nbt) continue;
+          int seen = 1;
+          if (lane == 0) {
             wc.d0 = tg; wc.d1 = bt;
-            if (!wait_flag_ge(&p.flags[(size_t)tg * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, tg, bt)) {
-              *dead = 1; ok = false; break;
-            }
+            seen = wait_flag_ge(&p.flags[(size_t)tg * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, tg, bt) ? 1 : 0;
             if (j == 0) RTRACE(st * 8 + 0, (long long)clock64());
-            fence_proxy_async();
-            const int row0 = bt * RB, col0 = (int)r * H;
-            for (int kc = 0; kc < KC; ++kc) {
-              if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
+          }
+          seen = __shfl_sync(0xffffffffu, seen, 0);
+          if (!seen) { *dead = 1; ok = false; break; }
+          fence_proxy_async();
+          const int row0 = bt * RB, col0 = (int)r * H;
+          bool lane_ok = true;
+          if (lane < nacc) {
+            // this lane owns ring stages == lane (mod nacc): the item's chunks that land there
+            for (int kc = (lane + nacc - gs % nacc) % nacc; kc < KC; kc += nacc) {
+              int s = gs + kc;
+              uint32_t ph = gph;
+              while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
+              if (!mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
               tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmG, &full[s], col0 + kc * RK, row0, tg);
-              if (++s == R_STAGES) { s = 0; ph ^= 1; }
             }
           }
+          if (__any_sync(0xffffffffu, !lane_ok)) { ok = false; break; }
+          gs += KC;
+          while (gs >= R_STAGES) { gs -= R_STAGES; gph ^= 1; }
         }
       }
     }
   } else if (warp < FIRST_EPI) {
-    // ---------------------------------------------------------------- MMA issuers
+    // ---------------------------------------------------------------- MMA issuers (own whole chunks)
     const int x = warp - 1;
     if (lane == 0) {
       constexpr uint64_t descA = smem_desc_base(16, 1024);       // d_ifgo tile, K-major
       constexpr uint64_t descB = smem_desc_base(8192, 1024);     // Wh chunk, N-major (64 units wide)
       const uint32_t idesc = instr_desc(p.fmt, 0, 1, RB, N);
-      bool ok = mbar_wait(w_full, 0, wc);
-      int s = 0;
-      uint32_t ph = 0;
+      bool ok = (x < nacc) && mbar_wait(w_full, 0, wc);
+      int gs = 0;
+      uint32_t gph = 0;
       uint32_t acc_ph[2] = {0, 0};
       int it = 0;
       const uint32_t w_addr = smem_u32(w_s);
@@ -636,19 +698,28 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             acc_ph[a] ^= 1;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + a * ACC_STRIDE + x * N;
-            for (int kc = 0; kc < KC; ++kc) {
-              if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
-              if (x == 0) mbar_expect_tx(&full[s], R_STAGE_BYTES);   // arm the stage's next use
-              if (kc == 0 && j == 0 && x == 0) RTRACE(st * 8 + 1, (long long)clock64());
+            uint32_t acc_on = 0;
+            for (int kc = (x + nacc - gs % nacc) % nacc; kc < KC; kc += nacc) {
+              int s = gs + kc;
+              uint32_t ph = gph;
+              while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
+              if (!mbar_wait_spin(&full[s], ph, wc)) { ok = false; break; }
+              mbar_expect_tx(&full[s], R_STAGE_BYTES);   // arm the stage's next use
+              if (kc == 0 && j == 0) RTRACE(st * 8 + 1, (long long)clock64());
               tc_fence_after();
-              const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES) + x * 32;
-              const uint32_t sb = w_addr + (uint32_t)kc * 8192 + x * 2048;
-              umma_f16(d_tmem, smem_desc(descA, sa), smem_desc(descB, sb), idesc, kc > 0 ? 1u : 0u);
+              const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES);
+              const uint32_t sb = w_addr + (uint32_t)kc * 8192;
+#pragma unroll
+              for (int k = 0; k < RK / 16; ++k)
+                umma_f16(d_tmem, smem_desc(descA, sa + k * 32), smem_desc(descB, sb + k * 2048), idesc,
+                         (k > 0) ? 1u : acc_on);
+              acc_on = 1;
               umma_commit(&empty[s]);
-              if (++s == R_STAGES) { s = 0; ph ^= 1; }
             }
             if (ok) umma_commit(&acc_full[a]);
             if (j == 0 && x == 0) RTRACE(st * 8 + 2, (long long)clock64());
+            gs += KC;
+            while (gs >= R_STAGES) { gs -= R_STAGES; gph ^= 1; }
           }
         }
       }
@@ -752,9 +823,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               tmem_ld_wait();
               float sum[16];
 #pragma unroll
-              for (int u = 0; u < 16; ++u)
-                sum[u] = (__uint_as_float(v[0][u]) + __uint_as_float(v[1][u])) +
-                         (__uint_as_float(v[2][u]) + __uint_as_float(v[3][u]));
+              for (int u = 0; u < 16; ++u) {
+                float a0 = __uint_as_float(v[0][u]);
+                if (nacc > 1) a0 += __uint_as_float(v[1][u]);
+                if (nacc > 2) a0 += __uint_as_float(v[2][u]);
+                if (nacc > 3) a0 += __uint_as_float(v[3][u]);
+                sum[u] = a0;
+              }
               if (dst == (int)r) {
 #pragma unroll
                 for (int u = 0; u < 16; ++u) own[u] = sum[u];
@@ -958,6 +1033,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   p.T = T; p.B = B; p.H = H;
   p.nbt = pl.nbt; p.nh = pl.nh; p.nb_par = pl.nb_par; p.ntl = pl.ntl;
   p.stages = pl.stages;
+  p.ni = pl.ni;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
   p.flag_target = pl.nh * pl.epi_warps;
@@ -1006,7 +1082,7 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   BLSTM_CUDA_OK(cudaMemsetAsync(ws, 0, pl.off_db, st));
   BwdParams p;
   p.T = T; p.B = B; p.H = H;
-  p.nbt = pl.nbt; p.nug = pl.nug; p.nb_par = pl.nb_par; p.ntl = pl.ntl; p.stages = pl.stages;
+  p.nbt = pl.nbt; p.nug = pl.nug; p.nb_par = pl.nb_par; p.ntl = pl.ntl; p.stages = pl.stages; p.ni = pl.ni;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
   p.flag_target = (H / 16) * 4;
