@@ -44,7 +44,7 @@ __device__ long long g_rtrace[16384];
 // to lane / issuer s % NI, which needs NI | R.  NI is also capped by the TMEM accumulators
 // available (max_ni) and by the chunks per item (an issuer without work would leave a stale
 // accumulator).
-static bool pick_ring(size_t fixed_bytes, int max_ni, int kc, int* stages, int* ni) {
+static bool pick_ring(size_t fixed_bytes, size_t stage_bytes, int max_ni, int kc, int* stages, int* ni) {
   // Prefer many concurrent issuers, but only count them fully when the ring holds two rounds of
   // their chunks (R >= 2 NI): with R == NI the loads of one round cannot overlap the MMAs of the
   // previous one.
@@ -52,7 +52,7 @@ static bool pick_ring(size_t fixed_bytes, int max_ni, int kc, int* stages, int* 
   int best_r = 0, best_n = 0, best_score = -1;
   for (int i = 0; i < 5; ++i) {
     const int r = cand[i];
-    if (fixed_bytes + (size_t)r * R_STAGE_BYTES > 232448) continue;
+    if (fixed_bytes + (size_t)r * stage_bytes > 232448) continue;
     for (int n = 4; n >= 1; --n) {
       if (n > max_ni || n > kc || r % n != 0) continue;
       const int score = (r >= 2 * n) ? 2 * n : n;
@@ -67,8 +67,8 @@ static bool pick_ring(size_t fixed_bytes, int max_ni, int kc, int* stages, int* 
 
 struct RecPlan {
   bool ok;
-  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages, ni;
-  size_t w_bytes, smem;
+  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages, ni, ws;
+  size_t w_bytes, stage_bytes, smem;
   size_t off_flags, n_flags, ws_bytes;
 };
 
@@ -81,7 +81,7 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   if (phase != BLSTM_PHASE_FWD) return p;
   if (d.dtype != BLSTM_F16 && d.dtype != BLSTM_BF16) return p;
   const int H = d.hidden_size, B = d.batch;
-  if (H % 64 != 0 || H < 64 || H > 1024) return p;
+  if (H % 64 != 0 || H < 64 || H > 2048) return p;
   p.nbt = cdiv(B, RB);
   int UH = 16;
   if (H <= 512 && p.nbt * (H / 32) >= 74) UH = 32;   // enough tiles to fill the GPU with wider slices
@@ -96,10 +96,14 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.grid = p.nh * p.nb_par;
   p.epi_warps = 4 * (UH / 16);
   p.threads = 32 * (1 + 256 / p.N + p.epi_warps);   // producer + MMA issuers + epilogue
+  // Wh slice resident in shared memory when it fits next to a useful ring; otherwise (H > 1024)
+  // the slice is streamed through the ring with h, chunk by chunk, every step (it stays in L2)
   p.w_bytes = (size_t)p.N * H * 2;
-  const size_t fixed = 1024 + p.w_bytes + 256;
-  if (!pick_ring(fixed, 256 / p.N, H / RK, &p.stages, &p.ni)) return p;
-  p.smem = fixed + (size_t)p.stages * R_STAGE_BYTES;
+  p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;
+  p.stage_bytes = R_STAGE_BYTES + (p.ws ? (size_t)p.N * 128 : 0);
+  const size_t fixed = 1024 + (p.ws ? 0 : p.w_bytes) + 256;
+  if (!pick_ring(fixed, p.stage_bytes, 256 / p.N, H / RK, &p.stages, &p.ni)) return p;
+  p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)(d.seq_len + 1) * p.nbt;
   p.off_flags = sizeof(Control);
   p.ws_bytes = p.off_flags + round_up(p.n_flags * sizeof(int), 256);
@@ -112,6 +116,8 @@ struct FwdParams {
   int nbt, nh, nb_par, ntl;
   int stages;
   int ni;                   // TMA-issuing lanes = MMA-issuing warps in use
+  int ws;                   // 1: Wh slice streamed through the ring instead of resident
+  int stage_bytes;
   int fmt;
   int no_arrive;
   int flag_target;          // nh * epilogue warps
@@ -156,8 +162,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   const int KC = H / RK;                            // K chunks
   uint8_t* w_s = smem;                              // [KC][N rows][128 B]
   const int R_STAGES = p.stages;
-  uint8_t* a_s = smem + (size_t)N * H * 2;          // [stages][128 rows][128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * R_STAGE_BYTES);
+  const int SB = p.stage_bytes;                     // h chunk (16 KB) [+ Wh chunk when streamed]
+  uint8_t* a_s = smem + (p.ws ? 0 : (size_t)N * H * 2);   // [stages][h chunk | optional Wh chunk]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;                            // [R_MAX_STAGES]
   uint64_t* empty = bars + R_MAX_STAGES;            // [R_MAX_STAGES]
   uint64_t* acc_full = bars + 2 * R_MAX_STAGES;     // [2]
@@ -185,7 +192,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     mbar_init(w_full, 1);
     *dead = 0;
     fence_mbar_init();
-    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], R_STAGE_BYTES);
+    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmH);
   }
@@ -204,7 +211,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     // ---------------------------------------------------------------- TMA producer
     // One thread needs a few hundred clocks per cp.async.bulk.tensor issue, so p.ni lanes issue in
     // lockstep, each owning the ring stages congruent to its lane index.
-    if (lane == 0) {
+    if (lane == 0 && !p.ws) {
       // resident Wh slice: rows (gate g, unit ht*UH + u), all K, as KC chunks of [N][64]
       mbar_expect_tx(w_full, (uint32_t)((size_t)N * H * 2));
       for (int kc = 0; kc < KC; ++kc) tma_load_3d(w_s + (size_t)kc * N * 128, &tmW, w_full, kc * RK, ht * UH, 0);
@@ -238,7 +245,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
-              tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmH, &full[s], kc * RK, row0, t);
+              tma_load_3d(a_s + (size_t)s * SB, &tmH, &full[s], kc * RK, row0, t);
+              if (p.ws) tma_load_3d(a_s + (size_t)s * SB + R_STAGE_BYTES, &tmW, &full[s], kc * RK, ht * UH, 0);
               if (t == 100) RTRACE(8192 + 64 + kc, (long long)clock64());
             }
           }
@@ -257,7 +265,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       // Every tcgen05 instruction (mma or commit) costs this thread ~150 clocks of issue time, so
       // issuer x owns WHOLE chunks (kc = x, x+NACC, ...): four MMAs and one commit per chunk,
       // in parallel with the other issuers, each into its own accumulator.
-      bool ok = (x < nacc) && mbar_wait(w_full, 0, wc);
+      bool ok = (x < nacc) && (p.ws || mbar_wait(w_full, 0, wc));
       int gs = 0;
       uint32_t gph = 0;
       uint32_t acc_ph[2] = {0, 0};
@@ -280,12 +288,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait_spin(&full[s], ph, wc)) { ok = false; break; }
-              mbar_expect_tx(&full[s], R_STAGE_BYTES);   // arm the stage's next use
+              mbar_expect_tx(&full[s], SB);   // arm the stage's next use
               if (kc == 0) RTRACE(t * 8 + 2, (long long)clock64());
               if (t == 100) RTRACE(8192 + kc * 2, (long long)clock64());
               tc_fence_after();
-              const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES);
-              const uint32_t sb = w_addr + (uint32_t)kc * N * 128;
+              const uint32_t sa = smem_u32(a_s + (size_t)s * SB);
+              const uint32_t sb = p.ws ? sa + R_STAGE_BYTES : w_addr + (uint32_t)kc * N * 128;
 #pragma unroll
               for (int k = 0; k < RK / 16; ++k)
                 umma_f16(d_tmem, smem_desc(descK, sa + k * 32), smem_desc(descK, sb + k * 32), idesc,
@@ -499,8 +507,8 @@ constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x
 
 struct BwdPlan {
   bool ok;
-  int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni;
-  size_t w_bytes, recv_bytes, smem;
+  int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni, ws;
+  size_t w_bytes, recv_bytes, stage_bytes, smem;
   size_t off_flags, n_flags, off_db, ws_bytes;
 };
 
@@ -510,7 +518,7 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   if (d.flags & BLSTM_FLAG_FORCE_GENERIC) return p;
   if (d.dtype != BLSTM_F16 && d.dtype != BLSTM_BF16) return p;
   const int H = d.hidden_size, B = d.batch;
-  if (H % 64 != 0 || H < 64 || H > 1024) return p;
+  if (H % 64 != 0 || H < 64 || H > 2048) return p;
   p.nbt = cdiv(B, RB);
   p.nug = H / 64;
   const int per_tile = p.nug * 4;
@@ -522,14 +530,17 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.grid = p.nb_par * per_tile;
   p.threads = 32 * (1 + 4 + 4);
   p.w_bytes = (size_t)H * 128;
+  p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;                   // stream the Wh slice through the ring
+  p.stage_bytes = R_STAGE_BYTES + (p.ws ? 8192 : 0);
+  const size_t wres = p.ws ? 0 : p.w_bytes;
   p.recv_bytes = (size_t)p.TI * 2 * 3 * XSLOT_BYTES;       // receive slots + send staging
-  if (1024 + p.w_bytes + p.recv_bytes + 256 + 3 * R_STAGE_BYTES > 232448 && p.TI == 2) {
+  if (1024 + wres + p.recv_bytes + 256 + 3 * p.stage_bytes > 232448 && p.TI == 2) {
     p.TI = 1;                                               // not enough room to interleave two tiles
     p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
   }
-  const size_t fixed = 1024 + p.w_bytes + p.recv_bytes + 256;
-  if (!pick_ring(fixed, 4, H / RK, &p.stages, &p.ni)) return p;
-  p.smem = fixed + (size_t)p.stages * R_STAGE_BYTES;
+  const size_t fixed = 1024 + wres + p.recv_bytes + 256;
+  if (!pick_ring(fixed, p.stage_bytes, 4, H / RK, &p.stages, &p.ni)) return p;
+  p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)d.seq_len * p.nbt;
   p.off_flags = sizeof(Control);
   p.off_db = p.off_flags + round_up(p.n_flags * sizeof(int), 256);
@@ -543,6 +554,8 @@ struct BwdParams {
   int nbt, nug, nb_par, ntl;
   int stages;
   int ni;
+  int ws;
+  int stage_bytes;
   int fmt;
   int no_arrive;
   int flag_target;          // (H/16) CTAs per batch tile x 4 epilogue warps
@@ -585,10 +598,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   const int KC = H / RK;
   const int R_STAGES = p.stages;
   uint8_t* w_s = smem;                                        // [KC][64 k rows][128 B]
-  uint8_t* recv = smem + (size_t)H * 128;                     // [TI][3 senders][128 rows][64 B]
+  const int SB = p.stage_bytes;                               // d_ifgo chunk (16 KB) [+ Wh chunk when streamed]
+  uint8_t* recv = smem + (p.ws ? 0 : (size_t)H * 128);                     // [TI][3 senders][128 rows][64 B]
   uint8_t* stage = recv + (size_t)TI * 3 * XSLOT_BYTES;      // [TI][3 receivers][128 rows][64 B]
   uint8_t* a_s = stage + (size_t)TI * 3 * XSLOT_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * R_STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;
   uint64_t* empty = bars + R_MAX_STAGES;
   uint64_t* acc_full = bars + 2 * R_MAX_STAGES;
@@ -615,7 +629,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], EW); }   // xchg: one expect_tx arrival + tx bytes
     *dead = 0;
     fence_mbar_init();
-    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], R_STAGE_BYTES);
+    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmG);
   }
@@ -633,7 +647,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   // dh = d_ifgo[T-s] x Wh for its tile, then (s < T) does the gate maths of step t = T-1-s.
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (lane == 0 && !p.ws) {
       mbar_expect_tx(w_full, (uint32_t)((size_t)H * 128));
       for (int kc = 0; kc < KC; ++kc)
         tma_load_2d(w_s + (size_t)kc * 8192, &tmW, w_full, ugc * 64, (int)r * H + kc * RK);
@@ -665,7 +679,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
-              tma_load_3d(a_s + (size_t)s * R_STAGE_BYTES, &tmG, &full[s], col0 + kc * RK, row0, tg);
+              tma_load_3d(a_s + (size_t)s * SB, &tmG, &full[s], col0 + kc * RK, row0, tg);
+              if (p.ws) tma_load_2d(a_s + (size_t)s * SB + R_STAGE_BYTES, &tmW, &full[s], ugc * 64, col0 + kc * RK);
             }
           }
           if (__any_sync(0xffffffffu, !lane_ok)) { ok = false; break; }
@@ -681,7 +696,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       constexpr uint64_t descA = smem_desc_base(16, 1024);       // d_ifgo tile, K-major
       constexpr uint64_t descB = smem_desc_base(8192, 1024);     // Wh chunk, N-major (64 units wide)
       const uint32_t idesc = instr_desc(p.fmt, 0, 1, RB, N);
-      bool ok = (x < nacc) && mbar_wait(w_full, 0, wc);
+      bool ok = (x < nacc) && (p.ws || mbar_wait(w_full, 0, wc));
       int gs = 0;
       uint32_t gph = 0;
       uint32_t acc_ph[2] = {0, 0};
@@ -704,11 +719,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait_spin(&full[s], ph, wc)) { ok = false; break; }
-              mbar_expect_tx(&full[s], R_STAGE_BYTES);   // arm the stage's next use
+              mbar_expect_tx(&full[s], SB);   // arm the stage's next use
               if (kc == 0 && j == 0) RTRACE(st * 8 + 1, (long long)clock64());
               tc_fence_after();
-              const uint32_t sa = smem_u32(a_s + (size_t)s * R_STAGE_BYTES);
-              const uint32_t sb = w_addr + (uint32_t)kc * 8192;
+              const uint32_t sa = smem_u32(a_s + (size_t)s * SB);
+              const uint32_t sb = p.ws ? sa + R_STAGE_BYTES : w_addr + (uint32_t)kc * 8192;
 #pragma unroll
               for (int k = 0; k < RK / 16; ++k)
                 umma_f16(d_tmem, smem_desc(descA, sa + k * 32), smem_desc(descB, sb + k * 2048), idesc,
@@ -1034,6 +1049,8 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   p.nbt = pl.nbt; p.nh = pl.nh; p.nb_par = pl.nb_par; p.ntl = pl.ntl;
   p.stages = pl.stages;
   p.ni = pl.ni;
+  p.ws = pl.ws;
+  p.stage_bytes = (int)pl.stage_bytes;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
   p.flag_target = pl.nh * pl.epi_warps;
@@ -1083,6 +1100,7 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   BwdParams p;
   p.T = T; p.B = B; p.H = H;
   p.nbt = pl.nbt; p.nug = pl.nug; p.nb_par = pl.nb_par; p.ntl = pl.ntl; p.stages = pl.stages; p.ni = pl.ni;
+  p.ws = pl.ws; p.stage_bytes = (int)pl.stage_bytes;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
   p.flag_target = (H / 16) * 4;
