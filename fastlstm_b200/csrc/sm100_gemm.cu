@@ -85,7 +85,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* acc_empty = acc_full + 2;      // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* bias_s = reinterpret_cast<float*>(bars) + 32;   // [BN] fp32, 128 B past the barriers
+  T16* bias_s = reinterpret_cast<T16*>(reinterpret_cast<uint8_t*>(bars) + 128);   // [2][BN], 128 B past the barriers
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -195,22 +195,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (warp == 2 && lane == 0) TRACE(it * 8 + 4, (long long)globaltimer_ns());
       tc_fence_after();
       if (has_bias) {
-        // fp32 sum of the two bias vectors for this tile's 256 columns (zero past N), staged
-        // once per tile by the 128 epilogue threads
-        const int t128 = threadIdx.x - 64;
-        float* bdst = bias_s;
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // previous tile's readers are done
+        // bx + bh for this tile's 256 columns, rounded to the storage type (as the reference forms
+        // its bias, fastlstm/lstm.py:67) and zero past N.  EVERY epilogue warp writes the whole
+        // (identical) table into the buffer of this tile's parity and then only needs a warp-level
+        // sync: no cross-warp barrier can strand a warp.  Warps are never more than one tile apart
+        // (a TMEM buffer is re-issued only after all four released it), so two buffers suffice.
+        T16* bdst = bias_s + (it & 1) * BN;
+        const int cc = n0 + lane * 8;
+        uint32_t w[4] = {0, 0, 0, 0};
+        if (cc < p.N) {
+          uint4 v0 = make_uint4(0, 0, 0, 0), v1 = make_uint4(0, 0, 0, 0);
+          if (p.bias0) v0 = *reinterpret_cast<const uint4*>(reinterpret_cast<const T16*>(p.bias0) + cc);
+          if (p.bias1) v1 = *reinterpret_cast<const uint4*>(reinterpret_cast<const T16*>(p.bias1) + cc);
+          const uint32_t a0[4] = {v0.x, v0.y, v0.z, v0.w}, a1[4] = {v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int cc = n0 + t128 * 2 + j;
-          float b = 0.f;
-          if (cc < p.N) {
-            if (p.bias0) b += Elem<T16>::to_f(reinterpret_cast<const T16*>(p.bias0)[cc]);
-            if (p.bias1) b += Elem<T16>::to_f(reinterpret_cast<const T16*>(p.bias1)[cc]);
+          for (int j = 0; j < 4; ++j) {
+            const float2 f0 = unpack2<T16>(a0[j]), f1 = unpack2<T16>(a1[j]);
+            w[j] = pack2<T16>(f0.x + f1.x, f0.y + f1.y);
           }
-          bdst[t128 * 2 + j] = b;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        *reinterpret_cast<uint4*>(bdst + lane * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        __syncwarp();
       }
       const uint32_t taddr = tmem_base + a * BN + (uint32_t(q * 32) << 16);
       constexpr int CW = OUT_F32 ? 32 : 64;      // output columns per staged box (128 B per row)
@@ -229,10 +234,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tmem_ld_32x32(taddr + c + 32, r1);
           tmem_ld_wait();
           if (has_bias) {
-            const float2* bs = reinterpret_cast<const float2*>(bias_s + c);
+            const uint32_t* bs = reinterpret_cast<const uint32_t*>(bias_s + (it & 1) * BN + c);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float2 b0 = bs[j], b1 = bs[16 + j];
+              const float2 b0 = unpack2<T16>(bs[j]), b1 = unpack2<T16>(bs[16 + j]);
               v[j] = pack2<T16>(__uint_as_float(r0[2 * j]) + b0.x, __uint_as_float(r0[2 * j + 1]) + b0.y);
               v[16 + j] = pack2<T16>(__uint_as_float(r1[2 * j]) + b1.x, __uint_as_float(r1[2 * j + 1]) + b1.y);
             }
