@@ -242,7 +242,7 @@ def main():
     # launching stream); the slower one is the dominant kernel of the step and goes in "roofline"
     hbm_gbs, tflops, which = peaks()
     es = ESIZE[cfg["dtype"]]
-    d = _lib.Desc(_lib.DTYPE_CODE[cfg["dtype"]], T, B, H, H, 0, 0, 0)
+    d = _lib.Desc(_lib.DTYPE_CODE[cfg["dtype"]], T, B, H, H, 0 if cfg["bwd"] else _lib.FLAG_INFERENCE, 0, 0)
     st = torch.cuda.current_stream().cuda_stream
     Wh = model.weight_hh_l0.detach()
     pre = (torch.randn(T, B, 4 * H, device=dev) * 0.5).to(dt)
@@ -281,7 +281,8 @@ def main():
                                                         dg.data_ptr(), carries[0].data_ptr(), carries[1].data_ptr(), None,
                                                         wsb.data_ptr(), nwb, st), "bwd_recurrence"))
         del dg, wsb
-    alg_bytes = 10.0 * B * H * es * T + 4.0 * H * H * es       # 10*B*H*e per step + Wh once
+    per_step = 10.0 if cfg["bwd"] else 5.0                    # forward-only runs save nothing for backward
+    alg_bytes = per_step * B * H * es * T + 4.0 * H * H * es   # per_step*B*H*e per step + Wh once
     alg_flops = 8.0 * B * H * H * T
     hbm_time = alg_bytes / (hbm_gbs * 1e9)
     tensor_time = alg_flops / (tflops * 1e12)

@@ -16,6 +16,7 @@ F32, F16, BF16 = 0, 1, 2
 DTYPE_CODE = {"fp32": F32, "fp16": F16, "bf16": BF16}
 PHASE_FWD, PHASE_BWD = 0, 1
 FLAG_FORCE_GENERIC = 1
+FLAG_INFERENCE = 8
 
 OK = 0
 E_WAIT_TIMEOUT = 6

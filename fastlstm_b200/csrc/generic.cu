@@ -117,6 +117,7 @@ struct GenParams {
   int nbt, nh, nb_par;
   int w_in_smem;
   int no_arrive;  // test hook: skip the arrival so waits run out
+  int inference;  // forward only: skip the stores that only backward needs
   unsigned long long limit_ns;
   Control* ctl;
   int* flags;
@@ -207,12 +208,14 @@ gen_fwd_kernel(GenParams p, T* __restrict__ ifgo, const T* __restrict__ Wh, T* _
         __syncthreads();
       }
       if (ok) {
+        if (!p.inference) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) ifgo[grow + (size_t)g * H] = Elem<T>::from_f(a[g]);
+          for (int g = 0; g < 4; ++g) ifgo[grow + (size_t)g * H] = Elem<T>::from_f(a[g]);
+        }
         c = sigmoid_acc(a[1]) * c + sigmoid_acc(a[0]) * tanh_acc(a[2]);
         const float h = sigmoid_acc(a[3]) * tanh_acc(c);
         const size_t o1 = ((size_t)(t + 1) * B + brow) * H + unit;
-        cell[o1] = Elem<T>::from_f(c);
+        if (!p.inference || t == Tn - 1) cell[o1] = Elem<T>::from_f(c);
         out[o1] = Elem<T>::from_f(h);
       }
       __syncthreads();  // every store of this CTA for step t is issued
@@ -394,6 +397,7 @@ static GenParams make_params(const blstm_desc& d, const GenericPlan& pl, void* w
   p.nbt = pl.nbt; p.nh = pl.nh; p.nb_par = pl.nb_par;
   p.w_in_smem = pl.w_in_smem ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
+  p.inference = (d.flags & BLSTM_FLAG_INFERENCE) ? 1 : 0;
   p.limit_ns = d.wait_limit_us > 0 ? (unsigned long long)d.wait_limit_us * 1000ull : kDefaultWaitNs;
   p.ctl = reinterpret_cast<Control*>(ws);
   p.flags = reinterpret_cast<int*>(static_cast<char*>(ws) + pl.off_flags);

@@ -120,6 +120,7 @@ struct FwdParams {
   int stage_bytes;
   int fmt;
   int no_arrive;
+  int inference;            // skip the stores that only backward needs
   int flag_target;          // nh * epilogue warps
   unsigned long long limit_ns;
   Control* ctl;
@@ -447,7 +448,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             }
           }
           // off the critical path: final pre-activations and c[t+1], saved for backward
-          if (row_ok) {
+          // (inference: only the last cell state is needed, as c_n)
+          if (row_ok && p.inference && t == p.T - 1) {
+            uint32_t wc_[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) wc_[u] = pk2<T16>(c[j][2 * u], c[j][2 * u + 1]);
+            stg16(cell + o1, make_uint4(wc_[0], wc_[1], wc_[2], wc_[3]));
+            stg16(cell + o1 + 8, make_uint4(wc_[4], wc_[5], wc_[6], wc_[7]));
+          }
+          if (row_ok && !p.inference) {
             T16* gdst = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -1053,6 +1062,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   p.stage_bytes = (int)pl.stage_bytes;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
+  p.inference = (d.flags & BLSTM_FLAG_INFERENCE) ? 1 : 0;
   p.flag_target = pl.nh * pl.epi_warps;
   p.limit_ns = d.wait_limit_us > 0 ? (unsigned long long)d.wait_limit_us * 1000ull : kDefaultWaitNs;
   p.ctl = reinterpret_cast<Control*>(ws);

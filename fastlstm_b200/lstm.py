@@ -134,10 +134,12 @@ def plan_name(dtype, T, B, I, H, phase="fwd"):
 # ---------------------------------------------------------------------------
 # Operator functions (same names and argument meaning as the reference)
 # ---------------------------------------------------------------------------
-def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh):
+def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh, inference=False):
     """Forward of one layer.  x [T,B,I]; h0,c0 [B,H] or None; Wx [4H,I]; Wh [4H,H];
     bx,bh [4H] or None.  Returns (out[T+1,B,H], cell[T+1,B,H], ifgo[T,B,4H]);
-    slot 0 of out/cell is the initial state.  (fastlstm/lstm.py:31-146)"""
+    slot 0 of out/cell is the initial state.  (fastlstm/lstm.py:31-146)
+    inference=True: nothing is saved for backward - ifgo and cell[1..T-1] are left unwritten
+    (cell[T] is still c_n), which halves the bytes each step moves."""
     lib = _lib.load()
     if x.dim() == 2:
         x = x[None]
@@ -153,7 +155,7 @@ def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh):
         raise ValueError("h0 and c0 must both be given or both be None")
     _require(h0, "h0", dt, (B, H), dev)
     _require(c0, "c0", dt, (B, H), dev)
-    d = _desc(dt, T, B, I, H)
+    d = _desc(dt, T, B, I, H, _lib.FLAG_INFERENCE if inference else 0)
     with torch.cuda.device(dev):
         states = torch.empty((2, T + 1, B, H), device=dev, dtype=dt)
         out, cell = states.unbind(0)
@@ -239,10 +241,11 @@ class PersistentLSTMfn(torch.autograd.Function):
             h_0 = None if h_0 is None else h_0.to(target)
             c_0 = None if c_0 is None else c_0.to(target)
         x = x.contiguous()
+        inference = not any(ctx.needs_input_grad)     # no_grad / nothing requires grad: save nothing
         with torch.autograd.profiler.record_function("fastlstm_b200::fwd"):
             out, cell, ifgo = lstm_persistent_fwd(
                 x, None if h_0 is None else h_0.contiguous(), None if c_0 is None else c_0.contiguous(),
-                Wx.contiguous(), bx, Wh.contiguous(), bh)
+                Wx.contiguous(), bx, Wh.contiguous(), bh, inference=inference)
         ctx.h0_is_none = h_0 is None
         ctx.has_bias = (bx is not None, bh is not None)
         ctx.save_for_backward(x, out, cell, ifgo, Wx, Wh)

@@ -52,6 +52,10 @@ enum {
 enum {
   BLSTM_FLAG_FORCE_GENERIC = 1, /* use the CUDA-core kernels even where a tcgen05 kernel exists */
   BLSTM_FLAG_RESERVED = 2,
+  BLSTM_FLAG_INFERENCE = 8,     /* forward only: the recurrence does not write back the final
+                                   pre-activations nor cell[1..T-1] (nothing is saved for backward);
+                                   out[1..T] and cell[T] are still produced.  Halves the bytes a
+                                   step moves (5*B*H*e instead of 10*B*H*e). */
   BLSTM_FLAG_TEST_NO_ARRIVE = 4 /* test hook: CTAs never signal step completion, so every
                                    cross-CTA wait runs into wait_limit_us and the launch ends
                                    with BLSTM_E_WAIT_TIMEOUT in the control block (no fault) */

@@ -171,6 +171,21 @@ def test_zero_upstream_gradient_gives_zero_grads():
     assert not np.any(r["dx"]) and not np.any(r["grads"][0][0]) and not np.any(r["grads"][0][2])
 
 
+def test_inference_mode_matches_training_forward():
+    """Under no_grad nothing is saved for backward (BLSTM_FLAG_INFERENCE); outputs are bit-identical."""
+    for dtype, shape in (("fp32", (9, 20, 24, 40)), ("bf16", (12, 200, 256, 256))):
+        T, B, I, H = shape
+        case = make_case(61, T=T, B=B, I=I, H=H, L=2, dtype=dtype, h0_std=0.2)
+        m = build_module(case)
+        dt = TORCH_DT[dtype]
+        x = case["x"].cuda().to(dt)
+        st = (case["h0"].cuda().to(dt), case["c0"].cuda().to(dt))
+        y1, (h1, c1) = m(x.clone().requires_grad_(), st)
+        with torch.no_grad():
+            y2, (h2, c2) = m(x, st)
+        assert torch.equal(y1, y2) and torch.equal(h1, h2) and torch.equal(c1, c2)
+
+
 def test_autocast_matches_explicit_half():
     import fastlstm_b200 as F
     case = make_case(5, T=10, B=8, I=32, H=32, dtype="fp16")
