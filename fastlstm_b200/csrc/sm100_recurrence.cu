@@ -34,8 +34,10 @@ constexpr int R_STAGE_BYTES = RB * RK * 2;   // 16 KB
 #ifdef BLSTM_REC_TRACE
 __device__ long long g_rtrace[16384];
 #define RTRACE(i, v) do { if (blockIdx.x == 0 && (i) < 16384) g_rtrace[(i)] = (v); } while (0)
+#define RT2(k) do { if (st == 100 && j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(8192 + 256 + (k), (long long)clock64()); } while (0)
 #else
 #define RTRACE(i, v) do { } while (0)
+#define RT2(k) do { } while (0)
 #endif
 
 // Ring depth R and number of concurrent TMA-issuing lanes / MMA-issuing warps NI.  Every stage
@@ -537,7 +539,7 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.ntl = cdiv(p.nbt, p.nb_par);
   p.TI = p.ntl >= 2 ? 2 : 1;
   p.grid = p.nb_par * per_tile;
-  p.threads = 32 * (1 + 4 + 4);
+  p.threads = 0;                          // set below, once TI is final
   p.w_bytes = (size_t)H * 128;
   p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;                   // stream the Wh slice through the ring
   p.stage_bytes = R_STAGE_BYTES + (p.ws ? 8192 : 0);
@@ -548,7 +550,11 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
     p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
   }
   const size_t fixed = 1024 + wres + p.recv_bytes + 256;
-  if (!pick_ring(fixed, p.stage_bytes, 4, H / RK, &p.stages, &p.ni)) return p;
+  // warps: 1 producer + 3 MMA issuers + 2 epilogue warpgroups = 12 (3 per SM sub-partition, 168
+  // registers each); a 13th warp would cap every thread at 128 registers.
+  const int n_issuers = 3;
+  p.threads = 32 * (1 + n_issuers + 8);
+  if (!pick_ring(fixed, p.stage_bytes, n_issuers, H / RK, &p.stages, &p.ni)) return p;
   p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)d.seq_len * p.nbt;
   p.off_flags = sizeof(Control);
@@ -567,7 +573,7 @@ struct BwdParams {
   int stage_bytes;
   int fmt;
   int no_arrive;
-  int flag_target;          // (H/16) CTAs per batch tile x 4 epilogue warps
+  int flag_target;          // (H/16) CTAs per batch tile x 8 epilogue warps
   unsigned long long limit_ns;
   Control* ctl;
   int* flags;               // [T][nbt]: arrivals for d_ifgo[t]
@@ -588,6 +594,16 @@ __device__ __forceinline__ void unpack16(const uint4& v0, const uint4& v1, float
   for (int u = 0; u < 8; ++u) { const float2 t = cvt2<T16>(w[u]); f[2 * u] = t.x; f[2 * u + 1] = t.y; }
 }
 template <typename T16>
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int u = 0; u < 4; ++u) { const float2 t = cvt2<T16>(w[u]); f[2 * u] = t.x; f[2 * u + 1] = t.y; }
+}
+template <typename T16>
+__device__ __forceinline__ void store8(T16* dst, const float* f) {
+  stg16(dst, make_uint4(pk2<T16>(f[0], f[1]), pk2<T16>(f[2], f[3]), pk2<T16>(f[4], f[5]), pk2<T16>(f[6], f[7])));
+}
+template <typename T16>
 __device__ __forceinline__ void store16(T16* dst, const float (&f)[16]) {
   uint32_t w[8];
 #pragma unroll
@@ -597,10 +613,11 @@ __device__ __forceinline__ void store16(T16* dst, const float (&f)[16]) {
 }
 
 template <int TI, typename T16>
-__global__ void __launch_bounds__(288, 1)
+__global__ void __launch_bounds__(384, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, const BwdParams p) {
-  constexpr int N = 64, NACC = 4, ACC_STRIDE = 256;
-  constexpr int FIRST_EPI = 5, EW = 4;
+  constexpr int N = 64, NACC = 3, ACC_STRIDE = 256;   // NACC: MMA issuer warps
+  constexpr int FIRST_EPI = 1 + NACC;
+  constexpr int ITEM_WARPS = 8;                   // epilogue warps, all working on every item
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int H = p.H;
@@ -633,9 +650,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     // full[s] is armed (arrive + expected bytes) for its first use here and re-armed by the MMA issuer
     // that consumed it for every later use, which keeps that work out of the latency-bound TMA producer loop
     for (int s = 0; s < R_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], nacc); mbar_init(&acc_empty[a], EW); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], nacc); mbar_init(&acc_empty[a], ITEM_WARPS); }
     mbar_init(w_full, 1);
-    for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], EW); }   // xchg: one expect_tx arrival + tx bytes
+    for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], ITEM_WARPS); }   // xchg: one expect_tx arrival + tx bytes
     *dead = 0;
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
@@ -749,19 +766,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue: thread = batch row
+    // ---------------------------------------------------------------- epilogue: two warpgroups
+    // thread = (batch row, 8 units): the two warpgroups split the CTA's 16 units of every item, which
+    // halves the serial path of a step (accumulator read-out, gate maths) and keeps it free of spills.
+    constexpr int NU = 8;                        // units per thread
+    const int g = (warp - FIRST_EPI) >> 2;       // warpgroup = which half of the 16 units
+    const int uoff = g * NU;
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
-    const int unit0 = ugc * 64 + (int)r * 16;
+    const int unit0 = ugc * 64 + (int)r * 16 + uoff;
     const int swz = (row_in_tile >> 1) & 3;   // bank swizzle of the exchanged slices
     const size_t H4 = 4 * (size_t)H;
     const T16* ifgo = reinterpret_cast<const T16*>(p.ifgo);
     const T16* cell = reinterpret_cast<const T16*>(p.cell);
     const T16* dout = reinterpret_cast<const T16*>(p.dout);
     T16* dg = reinterpret_cast<T16*>(p.d_ifgo);
-    uint32_t acc_ph[2] = {0, 0};
+    const bool shipper = (warp == FIRST_EPI) && lane == 0;   // sends the staged slices
     uint32_t x_ph[2] = {0, 0}, s_ph[2] = {0, 0};
-    int it = 0;
+    int it = 0;                 // MMA items consumed so far: TMEM buffer it & 1, on its (it >> 1)-th use
     bool ok = true;
     // where this CTA's slices land in each peer, and the peers' exchange barriers
     uint32_t peer_recv[4], peer_bar[4];
@@ -772,49 +794,37 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       peer_bar[dst] = mapa_shared(smem_u32(&xchg[0]), dst);
     }
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
-      float dc[TI][16], dhc[TI][16];
-      uint4 pf[14];     // next item's inputs: 4 gates (8), c[t+1] (2), c[t] (2), dout[t] (2)
+      float dc[TI][NU], dhc[TI][NU];
+      uint4 pf[7];       // next item's inputs: gates i,f,g,o, c[t+1], c[t], dout[t]
 #pragma unroll
       for (int j = 0; j < TI; ++j) {
         const int bt = pb + (ch * TI + j) * p.nb_par;
         const int row = bt * RB + row_in_tile;
         const bool rok = bt < p.nbt && row < p.B;
-        if (rok && p.dc_n) {
-          const T16* src = reinterpret_cast<const T16*>(p.dc_n) + (size_t)row * H + unit0;
-          unpack16<T16>(ldg16(src), ldg16(src + 8), dc[j]);
-        } else {
 #pragma unroll
-          for (int u = 0; u < 16; ++u) dc[j][u] = 0.f;
-        }
-        if (rok && p.dh_n) {
-          const T16* src = reinterpret_cast<const T16*>(p.dh_n) + (size_t)row * H + unit0;
-          unpack16<T16>(ldg16(src), ldg16(src + 8), dhc[j]);
-        } else {
-#pragma unroll
-          for (int u = 0; u < 16; ++u) dhc[j][u] = 0.f;
-        }
+        for (int u = 0; u < NU; ++u) { dc[j][u] = 0.f; dhc[j][u] = 0.f; }
+        if (rok && p.dc_n) unpack8<T16>(ldg16(reinterpret_cast<const T16*>(p.dc_n) + (size_t)row * H + unit0), dc[j]);
+        if (rok && p.dh_n) unpack8<T16>(ldg16(reinterpret_cast<const T16*>(p.dh_n) + (size_t)row * H + unit0), dhc[j]);
       }
       auto prefetch = [&](int t, int bt) {
         const int row = bt * RB + row_in_tile;
         if (bt < p.nbt && row < p.B) {
-          const T16* g = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+          const T16* gsrc = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) { pf[2 * k] = ldg16(g + (size_t)k * H); pf[2 * k + 1] = ldg16(g + (size_t)k * H + 8); }
-          const T16* c1 = cell + ((size_t)(t + 1) * p.B + row) * H + unit0;
-          const T16* c0 = cell + ((size_t)t * p.B + row) * H + unit0;
-          const T16* dd = dout + ((size_t)t * p.B + row) * H + unit0;
-          pf[8] = ldg16(c1); pf[9] = ldg16(c1 + 8);
-          pf[10] = ldg16(c0); pf[11] = ldg16(c0 + 8);
-          pf[12] = ldg16(dd); pf[13] = ldg16(dd + 8);
+          for (int k = 0; k < 4; ++k) pf[k] = ldg16(gsrc + (size_t)k * H);
+          pf[4] = ldg16(cell + ((size_t)(t + 1) * p.B + row) * H + unit0);
+          pf[5] = ldg16(cell + ((size_t)t * p.B + row) * H + unit0);
+          pf[6] = ldg16(dout + ((size_t)t * p.B + row) * H + unit0);
         }
       };
-      // two items ahead the same inputs are only pulled into L2 (no registers to hold them yet)
+      // two items ahead the same inputs are only pulled into L2 (no registers to hold them yet);
+      // a 32-byte sector covers both warpgroups' halves, so one warpgroup issues them
       auto prefetch_far = [&](int t, int bt) {
         const int row = bt * RB + row_in_tile;
-        if (bt < p.nbt && row < p.B) {
-          const T16* g = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+        if (g == 0 && bt < p.nbt && row < p.B) {
+          const T16* gsrc = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) prefetch_l2(g + (size_t)k * H);
+          for (int k = 0; k < 4; ++k) prefetch_l2(gsrc + (size_t)k * H);
           prefetch_l2(cell + ((size_t)t * p.B + row) * H + unit0);
           prefetch_l2(dout + ((size_t)t * p.B + row) * H + unit0);
         }
@@ -830,51 +840,55 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           if (st > 0) {
             // ---- dh = (sum over the cluster's four K ranges of) d_ifgo[T-st] x Wh
             const int a = it & 1;
+            const uint32_t a_ph = (uint32_t)(it >> 1) & 1u;
             ++it;
             wc.d0 = T - st; wc.d1 = bt;
-            if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
-            acc_ph[a] ^= 1;
+            if (!mbar_wait(&acc_full[a], a_ph, wc)) { ok = false; break; }
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 3, (long long)clock64());
             tc_fence_after();
-            const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16);
-            float own[16];
+            RT2(0);
+            const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16) + uoff;
 #pragma unroll
             for (int dst = 0; dst < 4; ++dst) {
-              // the four issuers' partial accumulators for these 16 units: four loads, ONE wait
-              uint32_t v[NACC][16];
+              // the issuers' partial accumulators for these units: NACC loads, ONE wait
+              uint32_t v[NACC][NU];
 #pragma unroll
-              for (int xx = 0; xx < NACC; ++xx) tmem_ld_32x16(taddr + xx * N + dst * 16, v[xx]);
+              for (int xx = 0; xx < NACC; ++xx) tmem_ld_32x8(taddr + xx * N + dst * 16, v[xx]);
               tmem_ld_wait();
-              float sum[16];
+              RT2(1 + dst * 2);
+              float sum[NU];
 #pragma unroll
-              for (int u = 0; u < 16; ++u) {
+              for (int u = 0; u < NU; ++u) {
                 float a0 = __uint_as_float(v[0][u]);
                 if (nacc > 1) a0 += __uint_as_float(v[1][u]);
                 if (nacc > 2) a0 += __uint_as_float(v[2][u]);
-                if (nacc > 3) a0 += __uint_as_float(v[3][u]);
                 sum[u] = a0;
               }
               if (dst == (int)r) {
 #pragma unroll
-                for (int u = 0; u < 16; ++u) own[u] = sum[u];
+                for (int u = 0; u < NU; ++u) dhc[j][u] = sum[u];   // last step's carry is dead by now
               } else {
                 // stage the slice for peer `dst` locally (row = 64 B, 16-byte pieces XOR-swizzled)
                 uint8_t* sp = stage + ((size_t)j * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES +
                               row_in_tile * XROW_BYTES;
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4)
-                  *reinterpret_cast<float4*>(sp + ((c4 ^ swz) << 4)) =
+                for (int c4 = 0; c4 < NU / 4; ++c4)
+                  *reinterpret_cast<float4*>(sp + (((uoff >> 2) + c4) ^ swz) * 16) =
                       make_float4(sum[4 * c4], sum[4 * c4 + 1], sum[4 * c4 + 2], sum[4 * c4 + 3]);
               }
+              RT2(2 + dst * 2);
             }
             tc_fence_before();
             fence_proxy_async_smem();                 // staged slices -> visible to the bulk-copy engine
+            RT2(9);
             __syncwarp();
             if (lane == 0) { mbar_arrive(&acc_empty[a]); mbar_arrive(&staged[j]); }
-            // one thread ships the three slices once all four epilogue warps have staged theirs
+            RT2(10);
+            // one thread ships the three slices once all eight epilogue warps have staged their part
             // (bounded mbarrier wait, never a named barrier: a warp that gave up must not strand the rest)
-            if (warp == FIRST_EPI && lane == 0 && mbar_wait(&staged[j], s_ph[j], wc)) {
+            if (shipper && mbar_wait(&staged[j], s_ph[j], wc)) {
               mbar_expect_tx(&xchg[j], 3 * XSLOT_BYTES);      // what this CTA is about to receive
+              RT2(11);
 #pragma unroll
               for (int dst = 0; dst < 4; ++dst)
                 if (dst != (int)r)
@@ -889,52 +903,66 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 5, (long long)clock64());
             const uint8_t* rv = recv + (size_t)j * (3 * XSLOT_BYTES) + row_in_tile * XROW_BYTES;
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              const int off = (c4 ^ swz) << 4;
+            for (int c4 = 0; c4 < NU / 4; ++c4) {
+              const int off = (((uoff >> 2) + c4) ^ swz) * 16;
               const float4 s0 = *reinterpret_cast<const float4*>(rv + off);
               const float4 s1 = *reinterpret_cast<const float4*>(rv + XSLOT_BYTES + off);
               const float4 s2 = *reinterpret_cast<const float4*>(rv + 2 * XSLOT_BYTES + off);
-              dhc[j][4 * c4 + 0] = own[4 * c4 + 0] + s0.x + s1.x + s2.x;
-              dhc[j][4 * c4 + 1] = own[4 * c4 + 1] + s0.y + s1.y + s2.y;
-              dhc[j][4 * c4 + 2] = own[4 * c4 + 2] + s0.z + s1.z + s2.z;
-              dhc[j][4 * c4 + 3] = own[4 * c4 + 3] + s0.w + s1.w + s2.w;
+              dhc[j][4 * c4 + 0] += s0.x + s1.x + s2.x;
+              dhc[j][4 * c4 + 1] += s0.y + s1.y + s2.y;
+              dhc[j][4 * c4 + 2] += s0.z + s1.z + s2.z;
+              dhc[j][4 * c4 + 3] += s0.w + s1.w + s2.w;
             }
           }
           if (st < T) {
-            // ---- gate maths of step t for this thread's row and 16 units
+            // ---- gate maths of step t for this thread's row and 8 units, two per packed word
             const int t = T - 1 - st;
-            float pi[16], pf_[16], pg[16], po[16], c1[16], c0[16], dd[16];
-            unpack16<T16>(pf[0], pf[1], pi);
-            unpack16<T16>(pf[2], pf[3], pf_);
-            unpack16<T16>(pf[4], pf[5], pg);
-            unpack16<T16>(pf[6], pf[7], po);
-            unpack16<T16>(pf[8], pf[9], c1);
-            unpack16<T16>(pf[10], pf[11], c0);
-            unpack16<T16>(pf[12], pf[13], dd);
-            float qi[16], qf[16], qg[16], qo[16];
+            RT2(12);
+            const uint32_t wi[4] = {pf[0].x, pf[0].y, pf[0].z, pf[0].w};
+            const uint32_t wf[4] = {pf[1].x, pf[1].y, pf[1].z, pf[1].w};
+            const uint32_t wg[4] = {pf[2].x, pf[2].y, pf[2].z, pf[2].w};
+            const uint32_t wo[4] = {pf[3].x, pf[3].y, pf[3].z, pf[3].w};
+            const uint32_t w1[4] = {pf[4].x, pf[4].y, pf[4].z, pf[4].w};
+            const uint32_t w0[4] = {pf[5].x, pf[5].y, pf[5].z, pf[5].w};
+            const uint32_t wd[4] = {pf[6].x, pf[6].y, pf[6].z, pf[6].w};
+            uint32_t qi[4], qf[4], qg[4], qo[4];
 #pragma unroll
-            for (int u = 0; u < 16; ++u) {
-              const float si = sigmoid_fast(pi[u]), sf = sigmoid_fast(pf_[u]), so = sigmoid_fast(po[u]);
-              const float tg = tanh_fast(pg[u]), tc = tanh_fast(c1[u]);
-              const float dh = dd[u] + dhc[j][u];
-              const float dcv = fmaf(dh * so, 1.f - tc * tc, dc[j][u]);
-              qi[u] = dcv * tg * si * (1.f - si);
-              qf[u] = dcv * c0[u] * sf * (1.f - sf);
-              qg[u] = dcv * si * (1.f - tg * tg);
-              qo[u] = dh * tc * so * (1.f - so);
-              dc[j][u] = dcv * sf;
+            for (int w = 0; w < 4; ++w) {
+              const float2 pi = cvt2<T16>(wi[w]), pff = cvt2<T16>(wf[w]), pg = cvt2<T16>(wg[w]), po = cvt2<T16>(wo[w]);
+              const float2 c1 = cvt2<T16>(w1[w]), c0 = cvt2<T16>(w0[w]), dd = cvt2<T16>(wd[w]);
+              float r_[2][4];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int u = 2 * w + e;
+                const float si = sigmoid_fast(e ? pi.y : pi.x), sf = sigmoid_fast(e ? pff.y : pff.x);
+                const float so = sigmoid_fast(e ? po.y : po.x);
+                const float tg = tanh_fast(e ? pg.y : pg.x), tc = tanh_fast(e ? c1.y : c1.x);
+                const float dh = (e ? dd.y : dd.x) + dhc[j][u];
+                const float dcv = fmaf(dh * so, 1.f - tc * tc, dc[j][u]);
+                r_[e][0] = dcv * tg * si * (1.f - si);
+                r_[e][1] = dcv * (e ? c0.y : c0.x) * sf * (1.f - sf);
+                r_[e][2] = dcv * si * (1.f - tg * tg);
+                r_[e][3] = dh * tc * so * (1.f - so);
+                dc[j][u] = dcv * sf;
+              }
+              qi[w] = pk2<T16>(r_[0][0], r_[1][0]);
+              qf[w] = pk2<T16>(r_[0][1], r_[1][1]);
+              qg[w] = pk2<T16>(r_[0][2], r_[1][2]);
+              qo[w] = pk2<T16>(r_[0][3], r_[1][3]);
             }
             if (row_ok) {
-              T16* dst = dg + ((size_t)t * p.B + row) * H4 + unit0;
-              store16<T16>(dst, qi);
-              store16<T16>(dst + (size_t)H, qf);
-              store16<T16>(dst + 2 * (size_t)H, qg);
-              store16<T16>(dst + 3 * (size_t)H, qo);
+              T16* dstp = dg + ((size_t)t * p.B + row) * H4 + unit0;
+              stg16(dstp, make_uint4(qi[0], qi[1], qi[2], qi[3]));
+              stg16(dstp + (size_t)H, make_uint4(qf[0], qf[1], qf[2], qf[3]));
+              stg16(dstp + 2 * (size_t)H, make_uint4(qg[0], qg[1], qg[2], qg[3]));
+              stg16(dstp + 3 * (size_t)H, make_uint4(qo[0], qo[1], qo[2], qo[3]));
             }
+            RT2(13);
             // publish d_ifgo[t] rows of this warp, then (after the release) fetch the next item's inputs
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 6, (long long)clock64());
             fence_proxy_async();
             __syncwarp();
+            RT2(14);
             if (lane == 0 && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)t * p.nbt + bt], 1);
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 7, (long long)clock64());
             {
@@ -947,8 +975,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             }
           } else if (row_ok) {
             // ---- after the last step: the carries are the gradients of the initial state
-            store16<T16>(reinterpret_cast<T16*>(p.dh0) + (size_t)row * H + unit0, dhc[j]);
-            store16<T16>(reinterpret_cast<T16*>(p.dc0) + (size_t)row * H + unit0, dc[j]);
+            store8<T16>(reinterpret_cast<T16*>(p.dh0) + (size_t)row * H + unit0, dhc[j]);
+            store8<T16>(reinterpret_cast<T16*>(p.dc0) + (size_t)row * H + unit0, dc[j]);
           }
         }
       }
@@ -1113,7 +1141,7 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   p.ws = pl.ws; p.stage_bytes = (int)pl.stage_bytes;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
-  p.flag_target = (H / 16) * 4;
+  p.flag_target = (H / 16) * 8;   // CTAs per batch tile x epilogue warps
   p.limit_ns = d.wait_limit_us > 0 ? (unsigned long long)d.wait_limit_us * 1000ull : kDefaultWaitNs;
   p.ctl = reinterpret_cast<Control*>(ws);
   p.flags = reinterpret_cast<int*>(static_cast<char*>(ws) + pl.off_flags);
