@@ -236,7 +236,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             }
             seen = __shfl_sync(0xffffffffu, seen, 0);
             if (!seen) { *dead = 1; ok = false; break; }
-            fence_proxy_async();   // peers' generic-proxy stores -> this lane's async-proxy (TMA) reads
+            // The peers' generic-proxy stores reach this lane's async-proxy (TMA) reads through the
+            // proxy fence each writer executes between its stores and its release (one fence on the
+            // causality path is enough; a second one here costs a memory round trip on the serial path).
             if (lane == 0) RTRACE(t * 8 + 1, (long long)clock64());
           }
           const int row0 = bt * RB;
@@ -695,7 +697,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           }
           seen = __shfl_sync(0xffffffffu, seen, 0);
           if (!seen) { *dead = 1; ok = false; break; }
-          fence_proxy_async();
+          // (the writers' proxy fence before their release covers the TMA reads below)
           const int row0 = bt * RB, col0 = (int)r * H;
           bool lane_ok = true;
           if (lane < nacc) {
