@@ -539,16 +539,23 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.nb_par = 148 / per_tile;
   if (p.nb_par > p.nbt) p.nb_par = p.nbt;
   p.ntl = cdiv(p.nbt, p.nb_par);
-  p.TI = p.ntl >= 2 ? 2 : 1;
+  // Batch tiles interleaved per CTA.  Their only per-tile state is the carries in registers: the
+  // exchange buffers below are indexed by item parity, not by tile.
+  p.TI = p.ntl >= 3 ? 4 : p.ntl >= 2 ? 2 : 1;
   p.grid = p.nb_par * per_tile;
-  p.threads = 0;                          // set below, once TI is final
+  p.threads = 0;                          // set below
   p.w_bytes = (size_t)H * 128;
   p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;                   // stream the Wh slice through the ring
   p.stage_bytes = R_STAGE_BYTES + (p.ws ? 8192 : 0);
   const size_t wres = p.ws ? 0 : p.w_bytes;
-  p.recv_bytes = (size_t)p.TI * 2 * 3 * XSLOT_BYTES;       // receive slots + send staging
-  if (1024 + wres + p.recv_bytes + 256 + 3 * p.stage_bytes > 232448 && p.TI == 2) {
-    p.TI = 1;                                               // not enough room to interleave two tiles
+  // Cluster exchange: receive slots (3 peers x 8 KB) and send staging (3 x 8 KB), each double
+  // buffered by item parity.  Every CTA of a cluster walks its items in the same order and waits for
+  // item n's slices before it stages item n+1, so slices of item n+2 cannot be sent (nor its staging
+  // reused) before item n has been consumed everywhere.  A single tile needs one buffer of each.
+  const int xbuf = p.TI >= 2 ? 2 : 1;
+  p.recv_bytes = (size_t)xbuf * 2 * 3 * XSLOT_BYTES;
+  if (1024 + wres + p.recv_bytes + 256 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
+    p.TI = 1;                                               // not enough room to interleave tiles
     p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
   }
   const size_t fixed = 1024 + wres + p.recv_bytes + 256;
@@ -619,6 +626,7 @@ __global__ void __launch_bounds__(384, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, const BwdParams p) {
   constexpr int N = 64, NACC = 3, ACC_STRIDE = 256;   // NACC: MMA issuer warps
   constexpr int FIRST_EPI = 1 + NACC;
+  constexpr bool WRITER_FENCE = (TI == 1);        // which side runs the generic->async proxy fence
   constexpr int ITEM_WARPS = 8;                   // epilogue warps, all working on every item
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -627,9 +635,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   const int R_STAGES = p.stages;
   uint8_t* w_s = smem;                                        // [KC][64 k rows][128 B]
   const int SB = p.stage_bytes;                               // d_ifgo chunk (16 KB) [+ Wh chunk when streamed]
-  uint8_t* recv = smem + (p.ws ? 0 : (size_t)H * 128);                     // [TI][3 senders][128 rows][64 B]
-  uint8_t* stage = recv + (size_t)TI * 3 * XSLOT_BYTES;      // [TI][3 receivers][128 rows][64 B]
-  uint8_t* a_s = stage + (size_t)TI * 3 * XSLOT_BYTES;
+  uint8_t* recv = smem + (p.ws ? 0 : (size_t)H * 128);                     // [XB][3 senders][128 rows][64 B]
+  constexpr int XB = TI >= 2 ? 2 : 1;                         // exchange buffers (by item parity)
+  uint8_t* stage = recv + (size_t)XB * 3 * XSLOT_BYTES;      // [XB][3 receivers][128 rows][64 B]
+  uint8_t* a_s = stage + (size_t)XB * 3 * XSLOT_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;
   uint64_t* empty = bars + R_MAX_STAGES;
@@ -697,7 +706,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           }
           seen = __shfl_sync(0xffffffffu, seen, 0);
           if (!seen) { *dead = 1; ok = false; break; }
-          // (the writers' proxy fence before their release covers the TMA reads below)
+          // One proxy fence must lie between the peers' generic-proxy stores and the TMA reads below.
+          // A single tile in flight is latency bound: the writers fence before their release (cheaper
+          // there).  Interleaved tiles are bound by the epilogue warps: the fence moves to this warp.
+          if (!WRITER_FENCE) fence_proxy_async();
           const int row0 = bt * RB, col0 = (int)r * H;
           bool lane_ok = true;
           if (lane < nacc) {
@@ -784,7 +796,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     const T16* dout = reinterpret_cast<const T16*>(p.dout);
     T16* dg = reinterpret_cast<T16*>(p.d_ifgo);
     const bool shipper = (warp == FIRST_EPI) && lane == 0;   // sends the staged slices
-    uint32_t x_ph[2] = {0, 0}, s_ph[2] = {0, 0};
     int it = 0;                 // MMA items consumed so far: TMEM buffer it & 1, on its (it >> 1)-th use
     bool ok = true;
     // where this CTA's slices land in each peer, and the peers' exchange barriers
@@ -843,6 +854,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             // ---- dh = (sum over the cluster's four K ranges of) d_ifgo[T-st] x Wh
             const int a = it & 1;
             const uint32_t a_ph = (uint32_t)(it >> 1) & 1u;
+            // exchange buffers and their barriers go by item parity too (one set for a single tile)
+            const int xb = (XB == 2) ? a : 0;
+            const uint32_t x_ph = (XB == 2) ? a_ph : ((uint32_t)it & 1u);
             ++it;
             wc.d0 = T - st; wc.d1 = bt;
             if (!mbar_wait(&acc_full[a], a_ph, wc)) { ok = false; break; }
@@ -871,7 +885,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                 for (int u = 0; u < NU; ++u) dhc[j][u] = sum[u];   // last step's carry is dead by now
               } else {
                 // stage the slice for peer `dst` locally (row = 64 B, 16-byte pieces XOR-swizzled)
-                uint8_t* sp = stage + ((size_t)j * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES +
+                uint8_t* sp = stage + ((size_t)xb * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES +
                               row_in_tile * XROW_BYTES;
 #pragma unroll
                 for (int c4 = 0; c4 < NU / 4; ++c4)
@@ -884,26 +898,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             fence_proxy_async_smem();                 // staged slices -> visible to the bulk-copy engine
             RT2(9);
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&acc_empty[a]); mbar_arrive(&staged[j]); }
+            if (lane == 0) { mbar_arrive(&acc_empty[a]); mbar_arrive(&staged[xb]); }
             RT2(10);
             // one thread ships the three slices once all eight epilogue warps have staged their part
             // (bounded mbarrier wait, never a named barrier: a warp that gave up must not strand the rest)
-            if (shipper && mbar_wait(&staged[j], s_ph[j], wc)) {
-              mbar_expect_tx(&xchg[j], 3 * XSLOT_BYTES);      // what this CTA is about to receive
+            if (shipper && mbar_wait(&staged[xb], x_ph, wc)) {
+              mbar_expect_tx(&xchg[xb], 3 * XSLOT_BYTES);      // what this CTA is about to receive
               RT2(11);
 #pragma unroll
               for (int dst = 0; dst < 4; ++dst)
                 if (dst != (int)r)
-                  dsmem_bulk_copy(peer_recv[dst] + j * (3 * XSLOT_BYTES),
-                                  stage + ((size_t)j * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES,
-                                  XSLOT_BYTES, peer_bar[dst] + j * 8);
+                  dsmem_bulk_copy(peer_recv[dst] + xb * (3 * XSLOT_BYTES),
+                                  stage + ((size_t)xb * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES,
+                                  XSLOT_BYTES, peer_bar[dst] + xb * 8);
             }
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 4, (long long)clock64());
-            s_ph[j] ^= 1;
-            if (!mbar_wait_cluster(&xchg[j], x_ph[j], wc)) { ok = false; break; }
-            x_ph[j] ^= 1;
+            if (!mbar_wait_cluster(&xchg[xb], x_ph, wc)) { ok = false; break; }
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 5, (long long)clock64());
-            const uint8_t* rv = recv + (size_t)j * (3 * XSLOT_BYTES) + row_in_tile * XROW_BYTES;
+            const uint8_t* rv = recv + (size_t)xb * (3 * XSLOT_BYTES) + row_in_tile * XROW_BYTES;
 #pragma unroll
             for (int c4 = 0; c4 < NU / 4; ++c4) {
               const int off = (((uoff >> 2) + c4) ^ swz) * 16;
@@ -962,7 +974,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             RT2(13);
             // publish d_ifgo[t] rows of this warp, then (after the release) fetch the next item's inputs
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 6, (long long)clock64());
-            fence_proxy_async();
+            if (WRITER_FENCE) fence_proxy_async();
             __syncwarp();
             RT2(14);
             if (lane == 0 && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)t * p.nbt + bt], 1);
@@ -1150,8 +1162,9 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   p.dout = dout; p.dh_n = dh_n; p.dc_n = dc_n; p.ifgo = ifgo; p.cell = cell;
   p.d_ifgo = d_ifgo; p.dh0 = dh0; p.dc0 = dc0;
   const bool bf = d.dtype == BLSTM_BF16;
-  if (pl.TI == 1) rc = bf ? launch_bwd_t<1, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<1, __half>(pl, tw, tg, p, st);
-  else            rc = bf ? launch_bwd_t<2, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<2, __half>(pl, tw, tg, p, st);
+  if (pl.TI == 1)      rc = bf ? launch_bwd_t<1, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<1, __half>(pl, tw, tg, p, st);
+  else if (pl.TI == 2) rc = bf ? launch_bwd_t<2, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<2, __half>(pl, tw, tg, p, st);
+  else                 rc = bf ? launch_bwd_t<4, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<4, __half>(pl, tw, tg, p, st);
   if (rc) return rc;
   if (db) {
     float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + pl.off_db);
