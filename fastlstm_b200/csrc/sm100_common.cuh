@@ -72,6 +72,15 @@ __device__ __forceinline__ void dsmem_bulk_copy(uint32_t remote_dst, const void*
       ::"r"(remote_dst), "r"(smem_u32(local_src)), "r"(bytes), "r"(remote_bar)
       : "memory");
 }
+// Counts one arrival on a CTA-local shared-memory counter (acquire-release, CTA scope) and returns
+// the count before it.  The warp whose arrival completes a group of `n` (a power of two) has, by the
+// release sequence on the counter, every earlier arriver's prior stores ordered before whatever it
+// releases next - so it alone publishes for the whole CTA.
+__device__ __forceinline__ uint32_t smem_count_arrive(int* counter) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(counter)) : "memory");
+  return old;
+}
 // arrive (release, cluster scope) on an mbarrier that lives in a peer CTA's shared memory
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t remote_bar_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");

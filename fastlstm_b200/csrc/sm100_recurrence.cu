@@ -94,17 +94,21 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.nb_par = 148 / p.nh;
   if (p.nb_par > p.nbt) p.nb_par = p.nbt;
   p.ntl = cdiv(p.nbt, p.nb_par);
-  p.TI = p.ntl >= 2 ? 2 : 1;
+  p.TI = p.ntl >= 3 ? 4 : p.ntl >= 2 ? 2 : 1;     // batch tiles interleaved per CTA (state: cell rows in registers)
+  if (UH == 32 && p.TI > 2) p.TI = 2;             // 16 units per thread: four tiles' cell rows would spill
   p.grid = p.nh * p.nb_par;
-  p.epi_warps = 4 * (UH / 16);
-  p.threads = 32 * (1 + 256 / p.N + p.epi_warps);   // producer + MMA issuers + epilogue
+  p.epi_warps = (UH == 16 && p.TI == 1) ? 4 : 8;
+  // a single tile in flight is latency bound and wants the 4th issuer (13 warps: 128 registers per
+  // thread, enough for one tile's state); interleaved tiles need 168 registers, hence 12 warps
+  const int n_issuers = UH == 16 ? (p.TI == 1 ? 4 : 3) : 2;
+  p.threads = 32 * (1 + n_issuers + p.epi_warps);   // producer + MMA issuers + epilogue
   // Wh slice resident in shared memory when it fits next to a useful ring; otherwise (H > 1024)
   // the slice is streamed through the ring with h, chunk by chunk, every step (it stays in L2)
   p.w_bytes = (size_t)p.N * H * 2;
   p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;
   p.stage_bytes = R_STAGE_BYTES + (p.ws ? (size_t)p.N * 128 : 0);
   const size_t fixed = 1024 + (p.ws ? 0 : p.w_bytes) + 256;
-  if (!pick_ring(fixed, p.stage_bytes, 256 / p.N, H / RK, &p.stages, &p.ni)) return p;
+  if (!pick_ring(fixed, p.stage_bytes, n_issuers, H / RK, &p.stages, &p.ni)) return p;
   p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)(d.seq_len + 1) * p.nbt;
   p.off_flags = sizeof(Control);
@@ -123,7 +127,8 @@ struct FwdParams {
   int fmt;
   int no_arrive;
   int inference;            // skip the stores that only backward needs
-  int flag_target;          // nh * epilogue warps
+  int flag_target;          // arrivals that complete a flag: nh CTAs per batch tile [x epilogue warps]
+  int cta_publish;          // 1: one arrival per CTA and item, 0: one per epilogue warp
   unsigned long long limit_ns;
   Control* ctl;
   int* flags;
@@ -153,12 +158,35 @@ __device__ __forceinline__ uint4 ldg16(const void* p) { return *reinterpret_cast
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void stg16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 
-// UH: hidden units per CTA (16 or 32).  TI: batch tiles interleaved per CTA (1 or 2).
+template <typename T16>
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int u = 0; u < 4; ++u) { const float2 t = cvt2<T16>(w[u]); f[2 * u] = t.x; f[2 * u + 1] = t.y; }
+}
+template <typename T16>
+__device__ __forceinline__ void store8(T16* dst, const float* f) {
+  stg16(dst, make_uint4(pk2<T16>(f[0], f[1]), pk2<T16>(f[2], f[3]), pk2<T16>(f[4], f[5]), pk2<T16>(f[6], f[7])));
+}
+template <int NCOL>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[NCOL]) {
+  if constexpr (NCOL == 16) tmem_ld_32x16(taddr, r); else tmem_ld_32x8(taddr, r);
+}
+
+// UH: hidden units per CTA (16 or 32).  TI: batch tiles interleaved per CTA (1, 2 or 4).
+// Warps: 1 TMA producer, NACC MMA issuers, 4 or 8 epilogue warps - at most 12 (3 per SM sub-partition),
+// which leaves 168 registers per thread; a 13th would cap them at 128.  The epilogue must not spill.
 template <int UH, int TI, typename T16>
-__global__ void __launch_bounds__(32 * (1 + 256 / (4 * UH) + 4 * (UH / 16)), 1)
+__global__ void __launch_bounds__(32 * (1 + (UH == 16 ? (TI == 1 ? 4 : 3) : 2) + (UH == 16 && TI == 1 ? 4 : 8)), 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmH, const FwdParams p) {
   constexpr int N = 4 * UH;
-  constexpr int EW = 4 * (UH / 16);                 // epilogue warps
+  // Epilogue warps.  A single tile of 16 units is latency bound and runs best as one warpgroup with
+  // 16 units per thread next to four issuers (9 warps); every other shape uses two warpgroups that
+  // split the CTA's units (8 or 16 per thread), which keeps interleaved tiles free of spills.
+  constexpr int EW = (UH == 16 && TI == 1) ? 4 : 8;
+  constexpr int NU = 4 * UH / EW;                   // units per epilogue thread
+  constexpr int NV = NU / 8;                        // 16-byte pieces per operand per thread
+  constexpr bool WRITER_FENCE = (TI == 1);          // which side runs the generic->async proxy fence
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int H = p.H;
@@ -175,15 +203,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint64_t* w_full = acc_empty + 2;                 // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 1);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* pub_cnt = const_cast<int*>(dead) + 1;        // [4] arrivals of the epilogue warps, by item index mod 4
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ht = blockIdx.x % p.nh, pb = blockIdx.x / p.nh;
   // One thread can issue a tcgen05.mma only every ~150 clocks whatever its shape, far below
   // what these small-N shapes need, so NACC warps issue concurrently: warp x takes the x-th
   // K=16 slice(s) of every chunk into its own TMEM accumulator, and the epilogue adds them up.
-  constexpr int NACC = 256 / N;                     // 4 for N=64, 2 for N=128
+  constexpr int NACC = (UH == 16) ? (TI == 1 ? 4 : 3) : 2;   // issuer warps / partial accumulators
   constexpr int FIRST_EPI = 1 + NACC;               // first epilogue warp
-  constexpr int ACC_STRIDE = NACC * N;              // columns per item buffer (256)
+  constexpr int ACC_STRIDE = 256;                   // columns per item buffer (NACC * N <= 256)
   constexpr uint32_t TMEM_COLS = 512;
   const int nacc = p.ni;                             // accumulators / issuers / TMA lanes in use
 
@@ -194,6 +223,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], nacc); mbar_init(&acc_empty[a], EW); }
     mbar_init(w_full, 1);
     *dead = 0;
+    for (int i = 0; i < 4; ++i) pub_cnt[i] = 0;
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
@@ -236,9 +266,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             }
             seen = __shfl_sync(0xffffffffu, seen, 0);
             if (!seen) { *dead = 1; ok = false; break; }
-            // The peers' generic-proxy stores reach this lane's async-proxy (TMA) reads through the
-            // proxy fence each writer executes between its stores and its release (one fence on the
-            // causality path is enough; a second one here costs a memory round trip on the serial path).
+            // One proxy fence must lie between the peers' generic-proxy stores and this warp's TMA
+            // reads.  A single tile in flight is latency bound: the writers fence before their release
+            // (cheaper there).  Interleaved tiles are bound by the epilogue warps: the fence runs here.
+            if (!WRITER_FENCE) fence_proxy_async();
             if (lane == 0) RTRACE(t * 8 + 1, (long long)clock64());
           }
           const int row0 = bt * RB;
@@ -317,135 +348,152 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    // thread = (batch row, NU units): warpgroup `ug` takes the ug-th group of NU of the CTA's UH units
     const int ew = warp - FIRST_EPI;
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    const int ug = ew >> 2;                 // which 16-unit group of the CTA's UH units
+    const int ug = ew >> 2;
     const int row_in_tile = q * 32 + lane;
-    const int unit0 = ht * UH + ug * 16;
+    const int unit0 = ht * UH + ug * NU;
     const size_t H4 = 4 * (size_t)H;
     T16* ifgo = reinterpret_cast<T16*>(p.ifgo);
     T16* out = reinterpret_cast<T16*>(p.out);
     T16* cell = reinterpret_cast<T16*>(p.cell);
-    uint32_t acc_ph[2] = {0, 0};
-    int it = 0;
+    int it = 0;                             // items consumed: TMEM buffer it & 1, on its (it >> 1)-th use
     bool ok = true;
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
-      float c[TI][16];
-      uint4 pre[8];                         // projected pre-activations of the NEXT item: 4 gates x 16 units
+      float c[TI][NU];
+      uint4 pre[4 * NV];                    // projected pre-activations of the NEXT item: 4 gates x NU units
       // initial cell state of this chunk's tiles
 #pragma unroll
       for (int j = 0; j < TI; ++j) {
         const int bt = pb + (ch * TI + j) * p.nb_par;
         const int row = bt * RB + row_in_tile;
+#pragma unroll
+        for (int u = 0; u < NU; ++u) c[j][u] = 0.f;
         if (bt < p.nbt && row < p.B) {
-          const uint4 v0 = ldg16(cell + (size_t)row * H + unit0), v1 = ldg16(cell + (size_t)row * H + unit0 + 8);
-          const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
-          for (int u = 0; u < 8; ++u) { const float2 f = cvt2<T16>(w[u]); c[j][2 * u] = f.x; c[j][2 * u + 1] = f.y; }
-        } else {
-#pragma unroll
-          for (int u = 0; u < 16; ++u) c[j][u] = 0.f;
+          for (int v = 0; v < NV; ++v) unpack8<T16>(ldg16(cell + (size_t)row * H + unit0 + 8 * v), &c[j][8 * v]);
         }
       }
-      // prefetch pre-activations of the first item
-      {
-        const int bt = pb + (ch * TI) * p.nb_par;
+      auto load_pre = [&](int t, int bt) {
         const int row = bt * RB + row_in_tile;
-        if (bt < p.nbt && row < p.B) {
-          const T16* src = ifgo + (size_t)row * H4 + unit0;
+        if (t < p.T && bt < p.nbt && row < p.B) {
+          const T16* src = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) { pre[2 * g] = ldg16(src + (size_t)g * H); pre[2 * g + 1] = ldg16(src + (size_t)g * H + 8); }
+          for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int v = 0; v < NV; ++v) pre[g * NV + v] = ldg16(src + (size_t)g * H + 8 * v);
         }
-      }
+      };
+      load_pre(0, pb + (ch * TI) * p.nb_par);   // pre-activations of the first item
       for (int t = 0; t < p.T && ok; ++t) {
 #pragma unroll
         for (int j = 0; j < TI; ++j) {
           const int bt = pb + (ch * TI + j) * p.nb_par;
           if (bt >= p.nbt) continue;
           const int a = it & 1;
+          const uint32_t a_ph = (uint32_t)(it >> 1) & 1u;
           ++it;
           const int row = bt * RB + row_in_tile;
           const bool row_ok = row < p.B;
           wc.d0 = t; wc.d1 = bt;
-          if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
-          acc_ph[a] ^= 1;
+          if (!mbar_wait(&acc_full[a], a_ph, wc)) { ok = false; break; }
           if (ew == 0 && lane == 0) RTRACE(t * 8 + 4, (long long)clock64());
           tc_fence_after();
-          const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16) + ug * 16;
-          uint32_t acc[4][16];
+          const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16) + ug * NU;
+          // The thread's NU units are worked in passes of PW: accumulator read-out (the issuers' partial
+          // sums, gate by gate, XG of them per wait so that at most 48 values are in flight), gate
+          // maths, h store.  Two interleaved tiles of 16 units per thread take two passes of 8 -
+          // a single pass would not fit the register file - and save the final pre-activations
+          // inside the pass; every other shape takes one pass and saves them after the release.
+          constexpr int PW = (NU == 16 && TI >= 2) ? 8 : NU;
+          constexpr int XG = (NACC * PW > 48) ? 2 : NACC;
+          const size_t o1 = ((size_t)(t + 1) * p.B + row) * H + unit0;
+          T16* gdst = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+          float pa[4][PW];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) tmem_ld_32x16(taddr + g * UH, acc[g]);
-          tmem_ld_wait();
+          for (int h0 = 0; h0 < NU; h0 += PW) {
 #pragma unroll
-          for (int x = 1; x < NACC; ++x) {
-            if (x >= nacc) break;
-            uint32_t part[4][16];
+            for (int g = 0; g < 4; ++g) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) tmem_ld_32x16(taddr + x * N + g * UH, part[g]);
-            tmem_ld_wait();
+              for (int x0 = 0; x0 < NACC; x0 += XG) {
+                uint32_t v[XG][PW];
+#pragma unroll
+                for (int x = 0; x < XG; ++x) tmem_ld_cols<PW>(taddr + (x0 + x) * N + g * UH + h0, v[x]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int u = 0; u < PW; ++u) {
+                  float s0 = (x0 == 0) ? 0.f : pa[g][u];
+#pragma unroll
+                  for (int x = 0; x < XG; ++x)
+                    if (x0 + x < nacc) s0 += __uint_as_float(v[x][u]);
+                  pa[g][u] = s0;
+                }
+              }
+            }
+            if (h0 + PW == NU) {
+              // the accumulator is in registers: hand the TMEM buffer back to the MMA warps
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[a]);
+              if (ew == 0 && lane == 0) RTRACE(t * 8 + 5, (long long)clock64());
+            }
 #pragma unroll
             for (int g = 0; g < 4; ++g)
 #pragma unroll
-              for (int u = 0; u < 16; ++u)
-                acc[g][u] = __float_as_uint(__uint_as_float(acc[g][u]) + __uint_as_float(part[g][u]));
-          }
-          // the accumulator is in registers: hand the TMEM buffer back to the MMA warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[a]);
-
-          if (ew == 0 && lane == 0) RTRACE(t * 8 + 5, (long long)clock64());
-          float pa[4][16];
+              for (int v = 0; v < PW / 8; ++v) {
+                const uint4 pw4 = pre[g * NV + h0 / 8 + v];
+                const uint32_t w[4] = {pw4.x, pw4.y, pw4.z, pw4.w};
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const uint32_t w[8] = {pre[2 * g].x, pre[2 * g].y, pre[2 * g].z, pre[2 * g].w,
-                                   pre[2 * g + 1].x, pre[2 * g + 1].y, pre[2 * g + 1].z, pre[2 * g + 1].w};
+                for (int u = 0; u < 4; ++u) {
+                  const float2 f2 = cvt2<T16>(w[u]);
+                  pa[g][8 * v + 2 * u] += f2.x;
+                  pa[g][8 * v + 2 * u + 1] += f2.y;
+                }
+              }
+            float hv[PW];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const float2 f = cvt2<T16>(w[u]);
-              pa[g][2 * u] = __uint_as_float(acc[g][2 * u]) + f.x;
-              pa[g][2 * u + 1] = __uint_as_float(acc[g][2 * u + 1]) + f.y;
+            for (int u = 0; u < PW; ++u) {
+              const float cn = sigmoid_fast(pa[1][u]) * c[j][h0 + u] + sigmoid_fast(pa[0][u]) * tanh_fast(pa[2][u]);
+              c[j][h0 + u] = cn;
+              hv[u] = sigmoid_fast(pa[3][u]) * tanh_fast(cn);
+            }
+            if (row_ok) {
+#pragma unroll
+              for (int v = 0; v < PW / 8; ++v) store8<T16>(out + o1 + h0 + 8 * v, &hv[8 * v]);
+              if (PW < NU && !p.inference) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) store8<T16>(gdst + (size_t)g * H + h0, pa[g]);
+              }
             }
           }
-          float hv[16];
-#pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const float cn = sigmoid_fast(pa[1][u]) * c[j][u] + sigmoid_fast(pa[0][u]) * tanh_fast(pa[2][u]);
-            c[j][u] = cn;
-            hv[u] = sigmoid_fast(pa[3][u]) * tanh_fast(cn);
-          }
-          const size_t o1 = ((size_t)(t + 1) * p.B + row) * H + unit0;
-          if (row_ok) {
-            uint32_t wh_[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) wh_[u] = pk2<T16>(hv[2 * u], hv[2 * u + 1]);
-            stg16(out + o1, make_uint4(wh_[0], wh_[1], wh_[2], wh_[3]));
-            stg16(out + o1 + 8, make_uint4(wh_[4], wh_[5], wh_[6], wh_[7]));
-          }
-          // publish h[t+1] first (it is all the peers wait for): generic-proxy stores -> proxy fence ->
-          // warp-level arrival with release semantics; peers read the rows through TMA
+          // publish h[t+1] first (it is all the peers wait for): generic-proxy stores -> proxy fence
+          // (here or on the reading side) -> warp-level arrival with release semantics; peers read
+          // the rows through TMA
           if (ew == 0 && lane == 0) RTRACE(t * 8 + 6, (long long)clock64());
-          fence_proxy_async();
+          if (WRITER_FENCE) fence_proxy_async();
           __syncwarp();
-          if (lane == 0 && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
+          // arrival per warp, or (cta_publish) one per CTA and item: the last epilogue warp to get here
+          // publishes for all (a warp can be at most two items ahead of another, so four counters
+          // never mix items)
+          if (lane == 0) {
+            const bool pub = !p.cta_publish || (smem_count_arrive(&pub_cnt[it & 3]) & (EW - 1)) == EW - 1;
+            if (pub && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
+          }
           if (ew == 0 && lane == 0) RTRACE(t * 8 + 7, (long long)clock64());
           // only now (after the release: a fence would otherwise wait for these loads) fetch the NEXT
           // item's projected pre-activations; they land while the peers run their step
           {
             int nj = j + 1, nt = t;
             if (nj == TI || pb + (ch * TI + nj) * p.nb_par >= p.nbt) { nj = 0; nt = t + 1; }
-            const int nbt_ = pb + (ch * TI + nj) * p.nb_par;
-            const int nrow = nbt_ * RB + row_in_tile;
-            if (nt < p.T && nrow < p.B) {
-              const T16* src = ifgo + ((size_t)nt * p.B + nrow) * H4 + unit0;
-#pragma unroll
-              for (int g = 0; g < 4; ++g) { pre[2 * g] = ldg16(src + (size_t)g * H); pre[2 * g + 1] = ldg16(src + (size_t)g * H + 8); }
-            }
-            // the item after that: only pull its lines into L2
+            load_pre(nt, pb + (ch * TI + nj) * p.nb_par);
+            // the item after that: only pull its lines into L2 (a 32-byte sector covers both
+            // warpgroups' pieces when each takes 16 bytes, so one of them asks)
             int fj = nj + 1, ft = nt;
             if (fj == TI || pb + (ch * TI + fj) * p.nb_par >= p.nbt) { fj = 0; ft = nt + 1; }
-            const int frow = (pb + (ch * TI + fj) * p.nb_par) * RB + row_in_tile;
-            if (ft < p.T && frow < p.B) {
+            const int fbt = pb + (ch * TI + fj) * p.nb_par;
+            const int frow = fbt * RB + row_in_tile;
+            if (ft < p.T && fbt < p.nbt && frow < p.B && (NV == 2 || ug == 0)) {
               const T16* src = ifgo + ((size_t)ft * p.B + frow) * H4 + unit0;
 #pragma unroll
               for (int g = 0; g < 4; ++g) prefetch_l2(src + (size_t)g * H);
@@ -453,28 +501,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           }
           // off the critical path: final pre-activations and c[t+1], saved for backward
           // (inference: only the last cell state is needed, as c_n)
-          if (row_ok && p.inference && t == p.T - 1) {
-            uint32_t wc_[8];
+          if (row_ok && (!p.inference || t == p.T - 1)) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) wc_[u] = pk2<T16>(c[j][2 * u], c[j][2 * u + 1]);
-            stg16(cell + o1, make_uint4(wc_[0], wc_[1], wc_[2], wc_[3]));
-            stg16(cell + o1 + 8, make_uint4(wc_[4], wc_[5], wc_[6], wc_[7]));
+            for (int v = 0; v < NV; ++v) store8<T16>(cell + o1 + 8 * v, &c[j][8 * v]);
           }
-          if (row_ok && !p.inference) {
-            T16* gdst = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+          if (PW == NU && row_ok && !p.inference) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint32_t w[8];
+            for (int g = 0; g < 4; ++g)
 #pragma unroll
-              for (int u = 0; u < 8; ++u) w[u] = pk2<T16>(pa[g][2 * u], pa[g][2 * u + 1]);
-              stg16(gdst + (size_t)g * H, make_uint4(w[0], w[1], w[2], w[3]));
-              stg16(gdst + (size_t)g * H + 8, make_uint4(w[4], w[5], w[6], w[7]));
-            }
-            uint32_t wc_[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) wc_[u] = pk2<T16>(c[j][2 * u], c[j][2 * u + 1]);
-            stg16(cell + o1, make_uint4(wc_[0], wc_[1], wc_[2], wc_[3]));
-            stg16(cell + o1 + 8, make_uint4(wc_[4], wc_[5], wc_[6], wc_[7]));
+              for (int v = 0; v < NV; ++v) store8<T16>(gdst + (size_t)g * H + 8 * v, &pa[g][8 * (v % (PW / 8))]);
           }
         }
       }
@@ -582,7 +617,8 @@ struct BwdParams {
   int stage_bytes;
   int fmt;
   int no_arrive;
-  int flag_target;          // (H/16) CTAs per batch tile x 8 epilogue warps
+  int flag_target;          // arrivals that complete a flag: H/16 CTAs per batch tile [x 8 epilogue warps]
+  int cta_publish;          // 1: one arrival per CTA and item, 0: one per epilogue warp
   unsigned long long limit_ns;
   Control* ctl;
   int* flags;               // [T][nbt]: arrivals for d_ifgo[t]
@@ -601,16 +637,6 @@ __device__ __forceinline__ void unpack16(const uint4& v0, const uint4& v1, float
   const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
   for (int u = 0; u < 8; ++u) { const float2 t = cvt2<T16>(w[u]); f[2 * u] = t.x; f[2 * u + 1] = t.y; }
-}
-template <typename T16>
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int u = 0; u < 4; ++u) { const float2 t = cvt2<T16>(w[u]); f[2 * u] = t.x; f[2 * u + 1] = t.y; }
-}
-template <typename T16>
-__device__ __forceinline__ void store8(T16* dst, const float* f) {
-  stg16(dst, make_uint4(pk2<T16>(f[0], f[1]), pk2<T16>(f[2], f[3]), pk2<T16>(f[4], f[5]), pk2<T16>(f[6], f[7])));
 }
 template <typename T16>
 __device__ __forceinline__ void store16(T16* dst, const float (&f)[16]) {
@@ -649,6 +675,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint64_t* staged = xchg + 2;                                // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(staged + 2);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* pub_cnt = const_cast<int*>(dead) + 1;        // [4] arrivals of the epilogue warps, by item index mod 4
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t r = cluster_ctarank();                       // gate whose K range this CTA owns
@@ -665,6 +692,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     mbar_init(w_full, 1);
     for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], ITEM_WARPS); }   // xchg: one expect_tx arrival + tx bytes
     *dead = 0;
+    for (int i = 0; i < 4; ++i) pub_cnt[i] = 0;
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
@@ -797,6 +825,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     T16* dg = reinterpret_cast<T16*>(p.d_ifgo);
     const bool shipper = (warp == FIRST_EPI) && lane == 0;   // sends the staged slices
     int it = 0;                 // MMA items consumed so far: TMEM buffer it & 1, on its (it >> 1)-th use
+    int pub_it = 0;             // gate-maths items published so far
     bool ok = true;
     // where this CTA's slices land in each peer, and the peers' exchange barriers
     uint32_t peer_recv[4], peer_bar[4];
@@ -977,7 +1006,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (WRITER_FENCE) fence_proxy_async();
             __syncwarp();
             RT2(14);
-            if (lane == 0 && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)t * p.nbt + bt], 1);
+            // arrival per warp, or (cta_publish) one per CTA and item: the last epilogue warp to get
+            // here publishes for all (a warp can be at most four items ahead of another - the
+            // maths-only items that open a chunk - so four counters never mix items)
+            if (lane == 0) {
+              const bool pub = !p.cta_publish ||
+                               (smem_count_arrive(&pub_cnt[pub_it & 3]) & (ITEM_WARPS - 1)) == ITEM_WARPS - 1;
+              if (pub && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)t * p.nbt + bt], 1);
+            }
+            ++pub_it;
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 7, (long long)clock64());
             {
               int nj = j + 1, ns = st;
@@ -1105,7 +1142,10 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
   p.inference = (d.flags & BLSTM_FLAG_INFERENCE) ? 1 : 0;
-  p.flag_target = pl.nh * pl.epi_warps;
+  // Hundreds of same-address reductions per flag serialise in L2, while electing one publisher per
+  // CTA adds a hop inside the CTA: per-CTA arrivals pay off from about a thousand per flag.
+  p.cta_publish = (pl.nh * pl.epi_warps >= 1024) ? 1 : 0;
+  p.flag_target = p.cta_publish ? pl.nh : pl.nh * pl.epi_warps;
   p.limit_ns = d.wait_limit_us > 0 ? (unsigned long long)d.wait_limit_us * 1000ull : kDefaultWaitNs;
   p.ctl = reinterpret_cast<Control*>(ws);
   p.flags = reinterpret_cast<int*>(static_cast<char*>(ws) + pl.off_flags);
@@ -1116,6 +1156,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
     return bf ? launch_fwd_t<U, I, __nv_bfloat16>(pl, tw, th, p, st) : launch_fwd_t<U, I, __half>(pl, tw, th, p, st);
   BLSTM_FWD_CASE(16, 1)
   BLSTM_FWD_CASE(16, 2)
+  BLSTM_FWD_CASE(16, 4)
   BLSTM_FWD_CASE(32, 1)
   BLSTM_FWD_CASE(32, 2)
 #undef BLSTM_FWD_CASE
@@ -1155,7 +1196,11 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   p.ws = pl.ws; p.stage_bytes = (int)pl.stage_bytes;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
-  p.flag_target = (H / 16) * 8;   // CTAs per batch tile x epilogue warps
+  // Hundreds of same-address reductions per flag serialise in L2, while electing one publisher per
+  // CTA adds a hop inside the CTA: per-CTA arrivals pay off from about a thousand per flag, and
+  // whenever tiles are interleaved (the epilogue warps are then the bottleneck).
+  p.cta_publish = ((H / 16) * 8 >= 1024 || pl.TI >= 2) ? 1 : 0;
+  p.flag_target = p.cta_publish ? H / 16 : (H / 16) * 8;
   p.limit_ns = d.wait_limit_us > 0 ? (unsigned long long)d.wait_limit_us * 1000ull : kDefaultWaitNs;
   p.ctl = reinterpret_cast<Control*>(ws);
   p.flags = reinterpret_cast<int*>(static_cast<char*>(ws) + pl.off_flags);
