@@ -549,7 +549,7 @@ static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensor
 // does (thread = batch row: dc carried in fp32 registers, d_ifgo[t-1] written and
 // published with the same per-(step, batch tile) arrival counters as the forward kernel).
 // =====================================================================================
-constexpr int DB_PARTS = 64;              // row groups of the bias-gradient column sum
+constexpr int DB_PARTS = 256;             // row groups of the bias-gradient column sum
 constexpr int XROW_BYTES = 64;            // one row of a slice: 16 fp32; its four 16-byte pieces are XOR-swizzled
 constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x 16 fp32 = 8 KB
 
@@ -827,14 +827,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     int it = 0;                 // MMA items consumed so far: TMEM buffer it & 1, on its (it >> 1)-th use
     int pub_it = 0;             // gate-maths items published so far
     bool ok = true;
-    // where this CTA's slices land in each peer, and the peers' exchange barriers
-    uint32_t peer_recv[4], peer_bar[4];
-#pragma unroll
-    for (int dst = 0; dst < 4; ++dst) {
-      const int slot = (int)r < dst ? (int)r : (int)r - 1;      // index of this source among dst's 3 senders
-      peer_recv[dst] = mapa_shared(smem_u32(recv) + slot * XSLOT_BYTES, dst);
-      peer_bar[dst] = mapa_shared(smem_u32(&xchg[0]), dst);
-    }
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
       float dc[TI][NU], dhc[TI][NU];
       uint4 pf[7];       // next item's inputs: gates i,f,g,o, c[t+1], c[t], dout[t]
@@ -871,7 +863,47 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           prefetch_l2(dout + ((size_t)t * p.B + row) * H + unit0);
         }
       };
+      // Everything in the gate maths that does not depend on dh is worked out ahead of the accumulator:
+      //   dh = dout + dh_carry;  dcv = dh*fA + dc;  d_i = dcv*fBi;  d_f = dcv*fBf;  d_g = dcv*fBg;
+      //   d_o = dh*fBo;  dc' = dcv*fSf
+      // With one tile in flight that happens as soon as the prefetched inputs land (the warps would
+      // only wait for the next accumulator); with interleaved tiles it fills the cluster exchange.
+      constexpr bool USE_FACTORS = (TI <= 2);
+      constexpr bool EARLY_FACTORS = (TI == 1);
+      constexpr int NF = USE_FACTORS ? NU : 1;
+      float fA[NF], fBi[NF], fBf[NF], fBg[NF], fBo[NF], fSf[NF], fDd[NF];
+      auto factors = [&]() {
+        if constexpr (USE_FACTORS) {
+        const uint32_t wi[4] = {pf[0].x, pf[0].y, pf[0].z, pf[0].w};
+        const uint32_t wf[4] = {pf[1].x, pf[1].y, pf[1].z, pf[1].w};
+        const uint32_t wg[4] = {pf[2].x, pf[2].y, pf[2].z, pf[2].w};
+        const uint32_t wo[4] = {pf[3].x, pf[3].y, pf[3].z, pf[3].w};
+        const uint32_t w1[4] = {pf[4].x, pf[4].y, pf[4].z, pf[4].w};
+        const uint32_t w0[4] = {pf[5].x, pf[5].y, pf[5].z, pf[5].w};
+        const uint32_t wd[4] = {pf[6].x, pf[6].y, pf[6].z, pf[6].w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float2 pi = cvt2<T16>(wi[w]), pff = cvt2<T16>(wf[w]), pg = cvt2<T16>(wg[w]), po = cvt2<T16>(wo[w]);
+          const float2 c1 = cvt2<T16>(w1[w]), c0 = cvt2<T16>(w0[w]), dd = cvt2<T16>(wd[w]);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int u = 2 * w + e;
+            const float si = sigmoid_fast(e ? pi.y : pi.x), sf = sigmoid_fast(e ? pff.y : pff.x);
+            const float so = sigmoid_fast(e ? po.y : po.x);
+            const float tg = tanh_fast(e ? pg.y : pg.x), tc = tanh_fast(e ? c1.y : c1.x);
+            fA[u] = so * (1.f - tc * tc);
+            fBi[u] = tg * si * (1.f - si);
+            fBf[u] = (e ? c0.y : c0.x) * sf * (1.f - sf);
+            fBg[u] = si * (1.f - tg * tg);
+            fBo[u] = tc * so * (1.f - so);
+            fSf[u] = sf;
+            fDd[u] = e ? dd.y : dd.x;
+          }
+        }
+        }
+      };
       prefetch(T - 1, pb + (ch * TI) * p.nb_par);
+      if (USE_FACTORS && EARLY_FACTORS) factors();
       for (int st = 0; st <= T && ok; ++st) {
 #pragma unroll
         for (int j = 0; j < TI; ++j) {
@@ -936,12 +968,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               RT2(11);
 #pragma unroll
               for (int dst = 0; dst < 4; ++dst)
-                if (dst != (int)r)
-                  dsmem_bulk_copy(peer_recv[dst] + xb * (3 * XSLOT_BYTES),
+                if (dst != (int)r) {
+                  // this CTA is sender number `slot` among peer dst's three; addresses mapped on the
+                  // spot (only this thread needs them)
+                  const int slot = (int)r < dst ? (int)r : (int)r - 1;
+                  dsmem_bulk_copy(mapa_shared(smem_u32(recv) + (xb * 3 + slot) * XSLOT_BYTES, dst),
                                   stage + ((size_t)xb * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES,
-                                  XSLOT_BYTES, peer_bar[dst] + xb * 8);
+                                  XSLOT_BYTES, mapa_shared(smem_u32(&xchg[xb]), dst));
+                }
             }
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 4, (long long)clock64());
+            if (USE_FACTORS && !EARLY_FACTORS && st < T) factors();     // fills the wait for the peers' slices
             if (!mbar_wait_cluster(&xchg[xb], x_ph, wc)) { ok = false; break; }
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 5, (long long)clock64());
             const uint8_t* rv = recv + (size_t)xb * (3 * XSLOT_BYTES) + row_in_tile * XROW_BYTES;
@@ -961,37 +998,61 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             // ---- gate maths of step t for this thread's row and 8 units, two per packed word
             const int t = T - 1 - st;
             RT2(12);
-            const uint32_t wi[4] = {pf[0].x, pf[0].y, pf[0].z, pf[0].w};
-            const uint32_t wf[4] = {pf[1].x, pf[1].y, pf[1].z, pf[1].w};
-            const uint32_t wg[4] = {pf[2].x, pf[2].y, pf[2].z, pf[2].w};
-            const uint32_t wo[4] = {pf[3].x, pf[3].y, pf[3].z, pf[3].w};
-            const uint32_t w1[4] = {pf[4].x, pf[4].y, pf[4].z, pf[4].w};
-            const uint32_t w0[4] = {pf[5].x, pf[5].y, pf[5].z, pf[5].w};
-            const uint32_t wd[4] = {pf[6].x, pf[6].y, pf[6].z, pf[6].w};
             uint32_t qi[4], qf[4], qg[4], qo[4];
+            if constexpr (USE_FACTORS) {
+              if (!EARLY_FACTORS && st == 0) factors();   // later items computed them during the exchange
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const float2 pi = cvt2<T16>(wi[w]), pff = cvt2<T16>(wf[w]), pg = cvt2<T16>(wg[w]), po = cvt2<T16>(wo[w]);
-              const float2 c1 = cvt2<T16>(w1[w]), c0 = cvt2<T16>(w0[w]), dd = cvt2<T16>(wd[w]);
-              float r_[2][4];
+              for (int w = 0; w < 4; ++w) {
+                float r_[2][4];
 #pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int u = 2 * w + e;
-                const float si = sigmoid_fast(e ? pi.y : pi.x), sf = sigmoid_fast(e ? pff.y : pff.x);
-                const float so = sigmoid_fast(e ? po.y : po.x);
-                const float tg = tanh_fast(e ? pg.y : pg.x), tc = tanh_fast(e ? c1.y : c1.x);
-                const float dh = (e ? dd.y : dd.x) + dhc[j][u];
-                const float dcv = fmaf(dh * so, 1.f - tc * tc, dc[j][u]);
-                r_[e][0] = dcv * tg * si * (1.f - si);
-                r_[e][1] = dcv * (e ? c0.y : c0.x) * sf * (1.f - sf);
-                r_[e][2] = dcv * si * (1.f - tg * tg);
-                r_[e][3] = dh * tc * so * (1.f - so);
-                dc[j][u] = dcv * sf;
+                for (int e = 0; e < 2; ++e) {
+                  const int u = 2 * w + e;
+                  const float dh = fDd[u] + dhc[j][u];
+                  const float dcv = fmaf(dh, fA[u], dc[j][u]);
+                  r_[e][0] = dcv * fBi[u];
+                  r_[e][1] = dcv * fBf[u];
+                  r_[e][2] = dcv * fBg[u];
+                  r_[e][3] = dh * fBo[u];
+                  dc[j][u] = dcv * fSf[u];
+                }
+                qi[w] = pk2<T16>(r_[0][0], r_[1][0]);
+                qf[w] = pk2<T16>(r_[0][1], r_[1][1]);
+                qg[w] = pk2<T16>(r_[0][2], r_[1][2]);
+                qo[w] = pk2<T16>(r_[0][3], r_[1][3]);
               }
-              qi[w] = pk2<T16>(r_[0][0], r_[1][0]);
-              qf[w] = pk2<T16>(r_[0][1], r_[1][1]);
-              qg[w] = pk2<T16>(r_[0][2], r_[1][2]);
-              qo[w] = pk2<T16>(r_[0][3], r_[1][3]);
+            } else {
+              // four interleaved tiles leave no registers for the factors: all of the maths here
+              const uint32_t wi[4] = {pf[0].x, pf[0].y, pf[0].z, pf[0].w};
+              const uint32_t wf[4] = {pf[1].x, pf[1].y, pf[1].z, pf[1].w};
+              const uint32_t wg[4] = {pf[2].x, pf[2].y, pf[2].z, pf[2].w};
+              const uint32_t wo[4] = {pf[3].x, pf[3].y, pf[3].z, pf[3].w};
+              const uint32_t w1[4] = {pf[4].x, pf[4].y, pf[4].z, pf[4].w};
+              const uint32_t w0[4] = {pf[5].x, pf[5].y, pf[5].z, pf[5].w};
+              const uint32_t wd[4] = {pf[6].x, pf[6].y, pf[6].z, pf[6].w};
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const float2 pi = cvt2<T16>(wi[w]), pff = cvt2<T16>(wf[w]), pg = cvt2<T16>(wg[w]), po = cvt2<T16>(wo[w]);
+                const float2 c1 = cvt2<T16>(w1[w]), c0 = cvt2<T16>(w0[w]), dd = cvt2<T16>(wd[w]);
+                float r_[2][4];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  const int u = 2 * w + e;
+                  const float si = sigmoid_fast(e ? pi.y : pi.x), sf = sigmoid_fast(e ? pff.y : pff.x);
+                  const float so = sigmoid_fast(e ? po.y : po.x);
+                  const float tg = tanh_fast(e ? pg.y : pg.x), tc = tanh_fast(e ? c1.y : c1.x);
+                  const float dh = (e ? dd.y : dd.x) + dhc[j][u];
+                  const float dcv = fmaf(dh * so, 1.f - tc * tc, dc[j][u]);
+                  r_[e][0] = dcv * (tg * si * (1.f - si));
+                  r_[e][1] = dcv * ((e ? c0.y : c0.x) * sf * (1.f - sf));
+                  r_[e][2] = dcv * (si * (1.f - tg * tg));
+                  r_[e][3] = dh * (tc * so * (1.f - so));
+                  dc[j][u] = dcv * sf;
+                }
+                qi[w] = pk2<T16>(r_[0][0], r_[1][0]);
+                qf[w] = pk2<T16>(r_[0][1], r_[1][1]);
+                qg[w] = pk2<T16>(r_[0][2], r_[1][2]);
+                qo[w] = pk2<T16>(r_[0][3], r_[1][3]);
+              }
             }
             if (row_ok) {
               T16* dstp = dg + ((size_t)t * p.B + row) * H4 + unit0;
@@ -1019,7 +1080,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             {
               int nj = j + 1, ns = st;
               if (nj == TI || pb + (ch * TI + nj) * p.nb_par >= p.nbt) { nj = 0; ns = st + 1; }
-              if (ns < T) prefetch(T - 1 - ns, pb + (ch * TI + nj) * p.nb_par);
+              if (ns < T) {
+                prefetch(T - 1 - ns, pb + (ch * TI + nj) * p.nb_par);
+                if (USE_FACTORS && EARLY_FACTORS) factors();
+              }
               int fj = nj + 1, fs = ns;
               if (fj == TI || pb + (ch * TI + fj) * p.nb_par >= p.nbt) { fj = 0; fs = ns + 1; }
               if (fs < T) prefetch_far(T - 1 - fs, pb + (ch * TI + fj) * p.nb_par);
@@ -1044,13 +1108,37 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 }
 
 // Column sums of d_ifgo [rows, cols] (16-bit) over DB_PARTS interleaved row groups -> part[DB_PARTS][cols].
+// HBM-bound (the whole d_ifgo is read once): a thread owns 8 adjacent columns (one 16-byte load per
+// row, a warp covers 512 contiguous bytes) and keeps 8 row loads in flight.
 template <typename T16>
 __global__ void __launch_bounds__(128) colsum_kernel(const T16* __restrict__ g, int rows, int cols, float* __restrict__ part) {
-  const int col = blockIdx.x * 128 + threadIdx.x;
+  const int col = (blockIdx.x * 128 + threadIdx.x) * 8;
   if (col >= cols) return;
-  float s = 0.f;
-  for (int rr = blockIdx.y; rr < rows; rr += DB_PARTS) s += Elem<T16>::to_f(g[(size_t)rr * cols + col]);
-  part[(size_t)blockIdx.y * cols + col] = s;
+  float s[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) s[u] = 0.f;
+  const T16* src = g + col;
+  int rr = blockIdx.y;
+  for (; rr + 7 * DB_PARTS < rows; rr += 8 * DB_PARTS) {
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = ldg16(src + (size_t)(rr + i * DB_PARTS) * cols);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { const float2 f = cvt2<T16>(w[u]); s[2 * u] += f.x; s[2 * u + 1] += f.y; }
+    }
+  }
+  for (; rr < rows; rr += DB_PARTS) {
+    const uint4 v = ldg16(src + (size_t)rr * cols);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { const float2 f = cvt2<T16>(w[u]); s[2 * u] += f.x; s[2 * u + 1] += f.y; }
+  }
+  float* dst = part + (size_t)blockIdx.y * cols + col;
+  *reinterpret_cast<float4*>(dst) = make_float4(s[0], s[1], s[2], s[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(s[4], s[5], s[6], s[7]);
 }
 
 template <int TI, typename T16>
@@ -1214,7 +1302,7 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   if (db) {
     float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + pl.off_db);
     const int rows = T * B, cols = 4 * H;
-    dim3 grid(cdiv(cols, 128), DB_PARTS);
+    dim3 grid(cdiv(cols, 1024), DB_PARTS);
     if (bf) colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)d_ifgo, rows, cols, part);
     else    colsum_kernel<__half><<<grid, 128, 0, st>>>((const __half*)d_ifgo, rows, cols, part);
     BLSTM_CUDA_OK(cudaGetLastError());
