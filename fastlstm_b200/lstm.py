@@ -280,18 +280,30 @@ def persistent_lstm(x, h_0, c_0, Wx, bx, Wh, bh):
 class FastLSTM(nn.Module):
     """nn.LSTM-style stacked LSTM on the B200 kernels (fastlstm/lstm.py:586-698).
 
-    Parameters have nn.LSTM's names, shapes, init distribution and RNG order
-    (weight_ih_l{k}, weight_hh_l{k}, bias_ih_l{k}, bias_hh_l{k}), so state dicts
-    are interchangeable with torch.nn.LSTM.  `version` is accepted for source
-    compatibility; only "persistent" exists here."""
+    Parameters have nn.LSTM's names, shapes, registration order, init distribution and RNG order
+    (weight_ih_l{k}[_reverse], weight_hh_l{k}[_reverse], bias_ih_l{k}[_reverse],
+    bias_hh_l{k}[_reverse]), so state dicts are interchangeable with torch.nn.LSTM.  `version` is
+    accepted for source compatibility; only "persistent" exists here.
+
+    Beyond the reference (which lists them as missing, README.md:92-93): `bidirectional` runs the
+    same kernels on the time-reversed input and concatenates the two directions' outputs
+    (states are ordered layer-major, direction-minor, like nn.LSTM); `dropout` is applied to
+    the outputs of every layer but the last while training.  `proj_size` is not implemented."""
 
     def __init__(self, input_size, hidden_size, num_layers=1, bias=True, batch_first=False,
-                 version="persistent", device=None, dtype=None):
+                 version="persistent", device=None, dtype=None, dropout=0.0, bidirectional=False,
+                 proj_size=0):
         super().__init__()
         if version != "persistent":
             raise ValueError(f"Not implemented: {version} (only 'persistent' exists)")
+        if proj_size != 0:
+            raise NotImplementedError("proj_size is not implemented")
+        if not 0.0 <= float(dropout) <= 1.0:
+            raise ValueError("dropout should be a number in range [0, 1]")
         self.input_size, self.hidden_size, self.num_layers = input_size, hidden_size, num_layers
         self.bias, self.batch_first, self.version = bias, batch_first, version
+        self.dropout, self.bidirectional = float(dropout), bool(bidirectional)
+        self.num_directions = 2 if bidirectional else 1
         k = 1.0 / hidden_size ** 0.5
         fk = dict(device=device, dtype=dtype)
 
@@ -299,14 +311,20 @@ class FastLSTM(nn.Module):
             return nn.Parameter(torch.rand(*shape, **fk) * 2 * k - k)
 
         for layer in range(num_layers):
-            setattr(self, f"weight_ih_l{layer}", u(4 * hidden_size, input_size if layer == 0 else hidden_size))
-            setattr(self, f"weight_hh_l{layer}", u(4 * hidden_size, hidden_size))
-            if bias:
-                setattr(self, f"bias_ih_l{layer}", u(4 * hidden_size))
-                setattr(self, f"bias_hh_l{layer}", u(4 * hidden_size))
+            in_l = input_size if layer == 0 else hidden_size * self.num_directions
+            for sfx in self._suffixes():
+                setattr(self, f"weight_ih_l{layer}{sfx}", u(4 * hidden_size, in_l))
+                setattr(self, f"weight_hh_l{layer}{sfx}", u(4 * hidden_size, hidden_size))
+                if bias:
+                    setattr(self, f"bias_ih_l{layer}{sfx}", u(4 * hidden_size))
+                    setattr(self, f"bias_hh_l{layer}{sfx}", u(4 * hidden_size))
 
-    def layer_params(self, layer):
-        g = lambda n: getattr(self, f"{n}_l{layer}", None)
+    def _suffixes(self):
+        return ("", "_reverse") if self.bidirectional else ("",)
+
+    def layer_params(self, layer, reverse=False):
+        sfx = "_reverse" if reverse else ""
+        g = lambda n: getattr(self, f"{n}_l{layer}{sfx}", None)
         return g("weight_ih"), g("bias_ih"), g("weight_hh"), g("bias_hh")
 
     def forward(self, x, h_c_0=None):
@@ -314,18 +332,29 @@ class FastLSTM(nn.Module):
             raise ValueError("expected a 3-D input [T,B,I] (or [B,T,I] with batch_first)")
         if self.batch_first:
             x = x.transpose(0, 1)
+        nd = self.num_directions
         if h_c_0 is None:
-            h_0 = c_0 = [None] * self.num_layers
+            h_0 = c_0 = [None] * (self.num_layers * nd)
         else:
             h_0, c_0 = h_c_0
             if h_0 is None or c_0 is None:
-                raise ValueError("h_c_0 must be a pair (h_0, c_0) of [num_layers, B, H] tensors or None")
+                raise ValueError("h_c_0 must be a pair (h_0, c_0) of [num_layers * num_directions, B, H] "
+                                 "tensors or None")
+            if len(h_0) != self.num_layers * nd or len(c_0) != self.num_layers * nd:
+                raise ValueError(f"expected {self.num_layers * nd} initial states, got {len(h_0)} / {len(c_0)}")
         h_n, c_n = [], []
         for layer in range(self.num_layers):
-            Wx, bx, Wh, bh = self.layer_params(layer)
-            x, h_i, c_i = PersistentLSTMfn.apply(x, h_0[layer], c_0[layer], Wx, bx, Wh, bh)
-            h_n.append(h_i)
-            c_n.append(c_i)
+            outs = []
+            for d in range(nd):
+                Wx, bx, Wh, bh = self.layer_params(layer, reverse=(d == 1))
+                x_d = x.flip(0) if d == 1 else x          # the reverse direction walks t = T-1 .. 0
+                o, h_i, c_i = PersistentLSTMfn.apply(x_d, h_0[layer * nd + d], c_0[layer * nd + d], Wx, bx, Wh, bh)
+                outs.append(o.flip(0) if d == 1 else o)
+                h_n.append(h_i)
+                c_n.append(c_i)
+            x = outs[0] if nd == 1 else torch.cat(outs, dim=-1)
+            if self.dropout > 0.0 and self.training and layer < self.num_layers - 1:
+                x = torch.nn.functional.dropout(x, self.dropout, True)
         if self.batch_first:
             x = x.transpose(0, 1)
         return x, (torch.stack(h_n), torch.stack(c_n))

@@ -1,0 +1,102 @@
+"""nn.LSTM options the reference lists as missing (README.md:92-93) and this module adds:
+`bidirectional` and inter-layer `dropout`.  Oracle: torch.nn.LSTM in float64 on the CPU with
+the same state dict (the comparison every reference test makes, tests/test_lstm.py:53,120,196)."""
+import numpy as np
+import pytest
+import torch
+
+from _util import TORCH_DT, max_rel
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair(I, H, L, dtype, seed, bidirectional=True, dropout=0.0, bias=True):
+    import fastlstm_b200 as F
+    torch.manual_seed(seed)
+    ref = torch.nn.LSTM(I, H, num_layers=L, bias=bias, bidirectional=bidirectional).double()
+    dt = TORCH_DT[dtype]
+    with torch.no_grad():                       # both sides see weights already rounded to `dtype`
+        for p in ref.parameters():
+            p.copy_(p.to(dt).double())
+    m = F.FastLSTM(I, H, num_layers=L, bias=bias, bidirectional=bidirectional, dropout=dropout,
+                   device="cuda", dtype=dt)
+    m.load_state_dict({k: v.to(dt) for k, v in ref.state_dict().items()})
+    return m, ref
+
+
+def _run_both(m, ref, T, B, I, H, L, dtype, seed, states=True):
+    dt = TORCH_DT[dtype]
+    nd = 2 if m.bidirectional else 1
+    g = torch.Generator().manual_seed(seed)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(dt).double()
+    x, dout = rnd(T, B, I), rnd(T, B, nd * H)
+    h0, c0 = rnd(L * nd, B, H) * 0.1, rnd(L * nd, B, H) * 0.1
+    h0, c0 = h0.to(dt).double(), c0.to(dt).double()
+    dhn, dcn = rnd(L * nd, B, H), rnd(L * nd, B, H)
+
+    def go(mod, cast):
+        xi = cast(x).requires_grad_(True)
+        st = (cast(h0).requires_grad_(True), cast(c0).requires_grad_(True)) if states else None
+        out, (hn, cn) = mod(xi, st)
+        torch.autograd.backward([out, hn, cn], [cast(dout), cast(dhn), cast(dcn)])
+        f = lambda t: t.detach().double().cpu().numpy()
+        res = {"out": f(out), "h_n": f(hn), "c_n": f(cn), "dx": f(xi.grad)}
+        if states:
+            res["dh0"], res["dc0"] = f(st[0].grad), f(st[1].grad)
+        for n, p in mod.named_parameters():
+            res["grad:" + n] = f(p.grad)
+        return res
+
+    got = go(m, lambda t: t.to("cuda", dt))
+    want = go(ref, lambda t: t.clone())
+    torch.cuda.synchronize()
+    return got, want
+
+
+def test_bidirectional_fp32_matches_nn_lstm():
+    import fastlstm_b200 as F
+    T, B, I, H, L = 9, 5, 11, 24, 2
+    m, ref = _pair(I, H, L, "fp32", seed=3)
+    got, want = _run_both(m, ref, T, B, I, H, L, "fp32", seed=4)
+    F.check_status()
+    assert got["out"].shape == (T, B, 2 * H) and got["h_n"].shape == (2 * L, B, H)
+    for k in want:
+        assert max_rel(got[k], want[k]) <= 1e-5, k
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_bidirectional_half_on_tensor_core_kernels(dtype):
+    import fastlstm_b200 as F
+    T, B, I, H, L = 12, 130, 64, 64, 2            # H % 64 == 0: the tcgen05 kernels run
+    m, ref = _pair(I, H, L, dtype, seed=5)
+    got, want = _run_both(m, ref, T, B, I, H, L, dtype, seed=6)
+    F.check_status()
+    for k in ("out", "h_n", "c_n"):
+        assert float(np.max(np.abs(got[k] - want[k]))) <= 2e-2, k
+    for k in want:
+        if k.startswith("grad:weight"):
+            e = float(np.linalg.norm(got[k] - want[k]) / np.linalg.norm(want[k]))
+            assert e <= 5e-2, (k, e)
+
+
+def test_dropout_only_acts_between_layers_while_training():
+    import fastlstm_b200 as F
+    T, B, I, H, L = 7, 6, 10, 16, 3
+    m, _ = _pair(I, H, L, "fp32", seed=7, bidirectional=False, dropout=0.5)
+    plain, _ = _pair(I, H, L, "fp32", seed=7, bidirectional=False, dropout=0.0)
+    x = torch.randn(T, B, I, device="cuda")
+    m.eval()
+    assert torch.equal(m(x)[0], plain(x)[0])                    # inactive in eval mode
+    m.train()
+    torch.manual_seed(11)
+    a = m(x)[0]
+    torch.manual_seed(11)
+    b = m(x)[0]
+    assert torch.equal(a, b) and not torch.equal(a, plain(x)[0])   # seeded, and it does drop
+    xg = x.clone().requires_grad_(True)
+    m(xg)[0].sum().backward()
+    assert torch.isfinite(xg.grad).all() and all(torch.isfinite(p.grad).all() for p in m.parameters())
+    one, _ = _pair(I, H, 1, "fp32", seed=7, bidirectional=False, dropout=0.5)
+    one.train()
+    assert torch.equal(one(x)[0], one(x)[0])                     # a single layer has nothing to drop
+    F.check_status()

@@ -38,3 +38,16 @@ def test_cpu_tensors_are_rejected_loudly():
 def test_unknown_version_rejected():
     with pytest.raises(ValueError):
         FastLSTM(4, 4, version="graph")
+
+
+def test_bidirectional_parameters_match_nn_lstm_and_options_are_validated():
+    m = FastLSTM(12, 8, num_layers=2, bidirectional=True, dropout=0.25)
+    ref = nn.LSTM(12, 8, num_layers=2, bidirectional=True, dropout=0.25)
+    assert [(n, tuple(p.shape)) for n, p in m.named_parameters()] == \
+           [(n, tuple(p.shape)) for n, p in ref.named_parameters()]
+    m.load_state_dict(ref.state_dict())
+    ref.load_state_dict(m.state_dict())
+    with pytest.raises(NotImplementedError):
+        FastLSTM(4, 4, proj_size=2)
+    with pytest.raises(ValueError):
+        FastLSTM(4, 4, dropout=1.5)
