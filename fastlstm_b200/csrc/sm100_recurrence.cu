@@ -589,15 +589,16 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   // reused) before item n has been consumed everywhere.  A single tile needs one buffer of each.
   const int xbuf = p.TI >= 2 ? 2 : 1;
   p.recv_bytes = (size_t)xbuf * 2 * 3 * XSLOT_BYTES;
-  if (1024 + wres + p.recv_bytes + 256 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
+  if (1024 + wres + p.recv_bytes + 384 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
     p.TI = 1;                                               // not enough room to interleave tiles
     p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
   }
-  const size_t fixed = 1024 + wres + p.recv_bytes + 256;
-  // warps: 1 producer + 3 MMA issuers + 2 epilogue warpgroups = 12 (3 per SM sub-partition, 168
-  // registers each); a 13th warp would cap every thread at 128 registers.
-  const int n_issuers = 3;
-  p.threads = 32 * (1 + n_issuers + 8);
+  const size_t fixed = 1024 + wres + p.recv_bytes + 384;    // 384: barriers and counters behind the ring
+  // warps: 1 producer + 3 MMA issuers (or 2 + a publisher warp when tiles are interleaved) + 2 epilogue
+  // warpgroups = 12 (3 per SM sub-partition, 168 registers each); a 13th warp would cap every thread
+  // at 128 registers.
+  const int n_issuers = p.TI >= 2 ? 2 : 3;
+  p.threads = 32 * 12;
   if (!pick_ring(fixed, p.stage_bytes, n_issuers, H / RK, &p.stages, &p.ni)) return p;
   p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)d.seq_len * p.nbt;
@@ -650,8 +651,14 @@ __device__ __forceinline__ void store16(T16* dst, const float (&f)[16]) {
 template <int TI, typename T16>
 __global__ void __launch_bounds__(384, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, const BwdParams p) {
-  constexpr int N = 64, NACC = 3, ACC_STRIDE = 256;   // NACC: MMA issuer warps
-  constexpr int FIRST_EPI = 1 + NACC;
+  // Warps: 0 = TMA producer, then NACC MMA issuers, then (interleaved tiles only) one PUBLISHER warp,
+  // then 8 epilogue warps from warp 4 on - 12 in all either way.
+  // With interleaved tiles the epilogue warps are the bottleneck, and the release that publishes an
+  // item stalls its thread for a memory round trip: there a thread of its own does the releasing
+  // (the epilogue warps only arrive on a CTA-local barrier after their stores), which costs one issuer.
+  constexpr bool PUBLISHER = (TI >= 2);
+  constexpr int N = 64, NACC = PUBLISHER ? 2 : 3, ACC_STRIDE = 256;   // NACC: MMA issuer warps
+  constexpr int FIRST_EPI = 4;
   constexpr bool WRITER_FENCE = (TI == 1);        // which side runs the generic->async proxy fence
   constexpr int ITEM_WARPS = 8;                   // epilogue warps, all working on every item
   extern __shared__ uint8_t smem_raw[];
@@ -676,6 +683,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(staged + 2);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* pub_cnt = const_cast<int*>(dead) + 1;        // [4] arrivals of the epilogue warps, by item index mod 4
+  uint64_t* pub_bar = reinterpret_cast<uint64_t*>(pub_cnt + 4);   // [4] item published? by item index mod 4
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t r = cluster_ctarank();                       // gate whose K range this CTA owns
@@ -693,6 +701,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], ITEM_WARPS); }   // xchg: one expect_tx arrival + tx bytes
     *dead = 0;
     for (int i = 0; i < 4; ++i) pub_cnt[i] = 0;
+    for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], ITEM_WARPS);
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
@@ -736,8 +745,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           if (!seen) { *dead = 1; ok = false; break; }
           // One proxy fence must lie between the peers' generic-proxy stores and the TMA reads below.
           // A single tile in flight is latency bound: the writers fence before their release (cheaper
-          // there).  Interleaved tiles are bound by the epilogue warps: the fence moves to this warp.
-          if (!WRITER_FENCE) fence_proxy_async();
+          // there).  With interleaved tiles neither the epilogue warps nor this warp can afford it
+          // (this loop then streams d_ifgo without a break): the writers' publisher warp runs it.
+          if (!WRITER_FENCE && !PUBLISHER) fence_proxy_async();
           const int row0 = bt * RB, col0 = (int)r * H;
           bool lane_ok = true;
           if (lane < nacc) {
@@ -757,7 +767,33 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
         }
       }
     }
-  } else if (warp < FIRST_EPI) {
+  } else if (PUBLISHER && warp == 1 + NACC) {
+    // ---------------------------------------------------------------- publisher
+    // Walks the gate-maths items in the epilogue's order; when all eight epilogue warps have stored
+    // an item's d_ifgo rows (their arrival on pub_bar is a CTA-scope release, this wait the acquire),
+    // one release at GPU scope counts this CTA in on the item's arrival counter.  An epilogue warp can
+    // be at most four items ahead of the slowest (it needs the counters this thread completes), so
+    // four barriers never mix items.
+    if (lane == 0) {
+      int k = 0;
+      bool ok = true;
+      for (int ch = 0; ch < n_chunks && ok; ++ch) {
+        for (int st = 0; st < T && ok; ++st) {
+          for (int j = 0; j < TI && ok; ++j) {
+            const int bt = pb + (ch * TI + j) * p.nb_par;
+            if (bt >= p.nbt) continue;
+            wc.d0 = T - 1 - st; wc.d1 = bt;
+            if (!mbar_wait(&pub_bar[k & 3], (uint32_t)(k >> 2) & 1u, wc)) { ok = false; break; }
+            // the generic->async proxy fence of the hand-off runs here, on the causality path between
+            // the epilogue warps' stores (ordered before this thread by the barrier) and the release
+            fence_proxy_async();
+            if (!p.no_arrive) red_release_gpu_add(&p.flags[(size_t)(T - 1 - st) * p.nbt + bt], 1);
+            ++k;
+          }
+        }
+      }
+    }
+  } else if (warp < 1 + NACC) {
     // ---------------------------------------------------------------- MMA issuers (own whole chunks)
     const int x = warp - 1;
     if (lane == 0) {
@@ -828,7 +864,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     int pub_it = 0;             // gate-maths items published so far
     bool ok = true;
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
-      float dc[TI][NU], dhc[TI][NU];
+      // dc is carried per interleaved tile; dh is rebuilt from the accumulator in every item, so one
+      // copy serves all tiles (its first value, the gradient of h_n, is fetched in the tile's first item)
+      float dc[TI][NU], dhc[NU];
       uint4 pf[7];       // next item's inputs: gates i,f,g,o, c[t+1], c[t], dout[t]
 #pragma unroll
       for (int j = 0; j < TI; ++j) {
@@ -836,9 +874,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
         const int row = bt * RB + row_in_tile;
         const bool rok = bt < p.nbt && row < p.B;
 #pragma unroll
-        for (int u = 0; u < NU; ++u) { dc[j][u] = 0.f; dhc[j][u] = 0.f; }
+        for (int u = 0; u < NU; ++u) dc[j][u] = 0.f;
         if (rok && p.dc_n) unpack8<T16>(ldg16(reinterpret_cast<const T16*>(p.dc_n) + (size_t)row * H + unit0), dc[j]);
-        if (rok && p.dh_n) unpack8<T16>(ldg16(reinterpret_cast<const T16*>(p.dh_n) + (size_t)row * H + unit0), dhc[j]);
       }
       auto prefetch = [&](int t, int bt) {
         const int row = bt * RB + row_in_tile;
@@ -938,12 +975,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               for (int u = 0; u < NU; ++u) {
                 float a0 = __uint_as_float(v[0][u]);
                 if (nacc > 1) a0 += __uint_as_float(v[1][u]);
-                if (nacc > 2) a0 += __uint_as_float(v[2][u]);
+                if (NACC > 2 && nacc > 2) a0 += __uint_as_float(v[NACC - 1][u]);
                 sum[u] = a0;
               }
               if (dst == (int)r) {
 #pragma unroll
-                for (int u = 0; u < NU; ++u) dhc[j][u] = sum[u];   // last step's carry is dead by now
+                for (int u = 0; u < NU; ++u) dhc[u] = sum[u];   // last step's carry is dead by now
               } else {
                 // stage the slice for peer `dst` locally (row = 64 B, 16-byte pieces XOR-swizzled)
                 uint8_t* sp = stage + ((size_t)xb * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES +
@@ -988,11 +1025,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               const float4 s0 = *reinterpret_cast<const float4*>(rv + off);
               const float4 s1 = *reinterpret_cast<const float4*>(rv + XSLOT_BYTES + off);
               const float4 s2 = *reinterpret_cast<const float4*>(rv + 2 * XSLOT_BYTES + off);
-              dhc[j][4 * c4 + 0] += s0.x + s1.x + s2.x;
-              dhc[j][4 * c4 + 1] += s0.y + s1.y + s2.y;
-              dhc[j][4 * c4 + 2] += s0.z + s1.z + s2.z;
-              dhc[j][4 * c4 + 3] += s0.w + s1.w + s2.w;
+              dhc[4 * c4 + 0] += s0.x + s1.x + s2.x;
+              dhc[4 * c4 + 1] += s0.y + s1.y + s2.y;
+              dhc[4 * c4 + 2] += s0.z + s1.z + s2.z;
+              dhc[4 * c4 + 3] += s0.w + s1.w + s2.w;
             }
+          }
+          if (st == 0) {
+#pragma unroll
+            for (int u = 0; u < NU; ++u) dhc[u] = 0.f;
+            if (row_ok && p.dh_n) unpack8<T16>(ldg16(reinterpret_cast<const T16*>(p.dh_n) + (size_t)row * H + unit0), dhc);
           }
           if (st < T) {
             // ---- gate maths of step t for this thread's row and 8 units, two per packed word
@@ -1007,7 +1049,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                   const int u = 2 * w + e;
-                  const float dh = fDd[u] + dhc[j][u];
+                  const float dh = fDd[u] + dhc[u];
                   const float dcv = fmaf(dh, fA[u], dc[j][u]);
                   r_[e][0] = dcv * fBi[u];
                   r_[e][1] = dcv * fBf[u];
@@ -1040,7 +1082,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                   const float si = sigmoid_fast(e ? pi.y : pi.x), sf = sigmoid_fast(e ? pff.y : pff.x);
                   const float so = sigmoid_fast(e ? po.y : po.x);
                   const float tg = tanh_fast(e ? pg.y : pg.x), tc = tanh_fast(e ? c1.y : c1.x);
-                  const float dh = (e ? dd.y : dd.x) + dhc[j][u];
+                  const float dh = (e ? dd.y : dd.x) + dhc[u];
                   const float dcv = fmaf(dh * so, 1.f - tc * tc, dc[j][u]);
                   r_[e][0] = dcv * (tg * si * (1.f - si));
                   r_[e][1] = dcv * ((e ? c0.y : c0.x) * sf * (1.f - sf));
@@ -1067,13 +1109,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (WRITER_FENCE) fence_proxy_async();
             __syncwarp();
             RT2(14);
-            // arrival per warp, or (cta_publish) one per CTA and item: the last epilogue warp to get
-            // here publishes for all (a warp can be at most four items ahead of another - the
-            // maths-only items that open a chunk - so four counters never mix items)
+            // interleaved tiles: hand the item to the publisher warp.  One tile: arrival per warp, or
+            // (cta_publish) one per CTA and item - the last epilogue warp to get here publishes for all
+            // (a warp can be at most four items ahead of another - the maths-only items that open a
+            // chunk - so four counters never mix items)
             if (lane == 0) {
-              const bool pub = !p.cta_publish ||
-                               (smem_count_arrive(&pub_cnt[pub_it & 3]) & (ITEM_WARPS - 1)) == ITEM_WARPS - 1;
-              if (pub && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)t * p.nbt + bt], 1);
+              if constexpr (PUBLISHER) {
+                mbar_arrive(&pub_bar[pub_it & 3]);      // the publisher warp releases for the CTA
+              } else {
+                const bool pub = !p.cta_publish ||
+                                 (smem_count_arrive(&pub_cnt[pub_it & 3]) & (ITEM_WARPS - 1)) == ITEM_WARPS - 1;
+                if (pub && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)t * p.nbt + bt], 1);
+              }
             }
             ++pub_it;
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 7, (long long)clock64());
@@ -1090,7 +1137,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             }
           } else if (row_ok) {
             // ---- after the last step: the carries are the gradients of the initial state
-            store8<T16>(reinterpret_cast<T16*>(p.dh0) + (size_t)row * H + unit0, dhc[j]);
+            store8<T16>(reinterpret_cast<T16*>(p.dh0) + (size_t)row * H + unit0, dhc);
             store8<T16>(reinterpret_cast<T16*>(p.dc0) + (size_t)row * H + unit0, dc[j]);
           }
         }
