@@ -98,10 +98,11 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   if (UH == 32 && p.TI > 2) p.TI = 2;             // 16 units per thread: four tiles' cell rows would spill
   p.grid = p.nh * p.nb_par;
   p.epi_warps = (UH == 16 && p.TI == 1) ? 4 : 8;
-  // a single tile in flight is latency bound and wants the 4th issuer (13 warps: 128 registers per
-  // thread, enough for one tile's state); interleaved tiles need 168 registers, hence 12 warps
-  const int n_issuers = UH == 16 ? (p.TI == 1 ? 4 : 3) : 2;
-  p.threads = 32 * (1 + n_issuers + p.epi_warps);   // producer + MMA issuers + epilogue
+  // a single 16-unit tile in flight is latency bound: four issuers next to one epilogue warpgroup
+  // (9 warps); otherwise two issuers, eight epilogue warps and, for interleaved tiles, the publisher
+  const int n_issuers = (UH == 16 && p.TI == 1) ? 4 : 2;
+  const int n_publisher = p.TI >= 2 ? 1 : 0;
+  p.threads = 32 * (1 + n_issuers + n_publisher + p.epi_warps);   // producer + MMA issuers [+ publisher] + epilogue
   // Wh slice resident in shared memory when it fits next to a useful ring; otherwise (H > 1024)
   // the slice is streamed through the ring with h, chunk by chunk, every step (it stays in L2)
   p.w_bytes = (size_t)p.N * H * 2;
@@ -174,10 +175,11 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[NCOL]
 }
 
 // UH: hidden units per CTA (16 or 32).  TI: batch tiles interleaved per CTA (1, 2 or 4).
-// Warps: 1 TMA producer, NACC MMA issuers, 4 or 8 epilogue warps - at most 12 (3 per SM sub-partition),
-// which leaves 168 registers per thread; a 13th would cap them at 128.  The epilogue must not spill.
+// Warps: 1 TMA producer, NACC MMA issuers, with interleaved tiles one publisher warp, 4 or 8 epilogue
+// warps - at most 12 (3 per SM sub-partition), which leaves 168 registers per thread; a 13th would cap
+// them at 128.  The epilogue must not spill.
 template <int UH, int TI, typename T16>
-__global__ void __launch_bounds__(32 * (1 + (UH == 16 ? (TI == 1 ? 4 : 3) : 2) + (UH == 16 && TI == 1 ? 4 : 8)), 1)
+__global__ void __launch_bounds__(32 * (UH == 16 && TI == 1 ? 9 : (TI >= 2 ? 12 : 11)), 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmH, const FwdParams p) {
   constexpr int N = 4 * UH;
   // Epilogue warps.  A single tile of 16 units is latency bound and runs best as one warpgroup with
@@ -204,14 +206,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 1);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* pub_cnt = const_cast<int*>(dead) + 1;        // [4] arrivals of the epilogue warps, by item index mod 4
+  uint64_t* pub_bar = reinterpret_cast<uint64_t*>(pub_cnt + 4);   // [4] item stored? by item index mod 4
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ht = blockIdx.x % p.nh, pb = blockIdx.x / p.nh;
   // One thread can issue a tcgen05.mma only every ~150 clocks whatever its shape, far below
   // what these small-N shapes need, so NACC warps issue concurrently: warp x takes the x-th
   // K=16 slice(s) of every chunk into its own TMEM accumulator, and the epilogue adds them up.
-  constexpr int NACC = (UH == 16) ? (TI == 1 ? 4 : 3) : 2;   // issuer warps / partial accumulators
-  constexpr int FIRST_EPI = 1 + NACC;               // first epilogue warp
+  // With interleaved tiles the epilogue warps are the bottleneck and the release that publishes an item
+  // stalls its thread for a memory round trip, so a PUBLISHER warp does the releasing (and the proxy
+  // fence of the hand-off): the epilogue warps only arrive on a CTA-local barrier after storing h.
+  constexpr bool PUBLISHER = (TI >= 2);
+  constexpr int NACC = (UH == 16 && TI == 1) ? 4 : 2;   // issuer warps / partial accumulators
+  constexpr int FIRST_EPI = 1 + NACC + (PUBLISHER ? 1 : 0);   // first epilogue warp
   constexpr int ACC_STRIDE = 256;                   // columns per item buffer (NACC * N <= 256)
   constexpr uint32_t TMEM_COLS = 512;
   const int nacc = p.ni;                             // accumulators / issuers / TMA lanes in use
@@ -224,6 +231,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     mbar_init(w_full, 1);
     *dead = 0;
     for (int i = 0; i < 4; ++i) pub_cnt[i] = 0;
+    for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], EW);
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
@@ -268,8 +276,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (!seen) { *dead = 1; ok = false; break; }
             // One proxy fence must lie between the peers' generic-proxy stores and this warp's TMA
             // reads.  A single tile in flight is latency bound: the writers fence before their release
-            // (cheaper there).  Interleaved tiles are bound by the epilogue warps: the fence runs here.
-            if (!WRITER_FENCE) fence_proxy_async();
+            // (cheaper there).  With interleaved tiles neither the epilogue warps nor this warp can afford
+            // it (this loop then streams h without a break): the writers' publisher warp runs it.
+            if (!WRITER_FENCE && !PUBLISHER) fence_proxy_async();
             if (lane == 0) RTRACE(t * 8 + 1, (long long)clock64());
           }
           const int row0 = bt * RB;
@@ -292,7 +301,31 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
         }
       }
     }
-  } else if (warp < FIRST_EPI) {
+  } else if (PUBLISHER && warp == 1 + NACC) {
+    // ---------------------------------------------------------------- publisher
+    // Walks the items in the epilogue's order; when all epilogue warps have stored an item's h rows
+    // (their arrival on pub_bar is a CTA-scope release, this wait the acquire), the proxy fence of the
+    // hand-off and one release at GPU scope count this CTA in on the item's arrival counter.  An
+    // epilogue warp can be at most four items ahead (it needs the counters this thread completes),
+    // so four barriers never mix items.
+    if (lane == 0) {
+      int k = 0;
+      bool ok = true;
+      for (int ch = 0; ch < n_chunks && ok; ++ch) {
+        for (int t = 0; t < p.T && ok; ++t) {
+          for (int j = 0; j < TI && ok; ++j) {
+            const int bt = pb + (ch * TI + j) * p.nb_par;
+            if (bt >= p.nbt) continue;
+            wc.d0 = t; wc.d1 = bt;
+            if (!mbar_wait(&pub_bar[k & 3], (uint32_t)(k >> 2) & 1u, wc)) { ok = false; break; }
+            fence_proxy_async();
+            if (!p.no_arrive) red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
+            ++k;
+          }
+        }
+      }
+    }
+  } else if (warp < 1 + NACC) {
     // ---------------------------------------------------------------- MMA issuers
     const int x = warp - 1;                 // accumulator / K-slice index of this issuer
     if (lane == 0) {
@@ -477,8 +510,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           // publishes for all (a warp can be at most two items ahead of another, so four counters
           // never mix items)
           if (lane == 0) {
-            const bool pub = !p.cta_publish || (smem_count_arrive(&pub_cnt[it & 3]) & (EW - 1)) == EW - 1;
-            if (pub && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
+            if constexpr (PUBLISHER) {
+              mbar_arrive(&pub_bar[(it - 1) & 3]);     // the publisher warp releases for the CTA
+            } else {
+              const bool pub = !p.cta_publish || (smem_count_arrive(&pub_cnt[it & 3]) & (EW - 1)) == EW - 1;
+              if (pub && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
+            }
           }
           if (ew == 0 && lane == 0) RTRACE(t * 8 + 7, (long long)clock64());
           // only now (after the release: a fence would otherwise wait for these loads) fetch the NEXT
@@ -1279,7 +1316,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   p.inference = (d.flags & BLSTM_FLAG_INFERENCE) ? 1 : 0;
   // Hundreds of same-address reductions per flag serialise in L2, while electing one publisher per
   // CTA adds a hop inside the CTA: per-CTA arrivals pay off from about a thousand per flag.
-  p.cta_publish = (pl.nh * pl.epi_warps >= 1024) ? 1 : 0;
+  p.cta_publish = (pl.nh * pl.epi_warps >= 1024 || pl.TI >= 2) ? 1 : 0;   // interleaved tiles: the publisher warp
   p.flag_target = p.cta_publish ? pl.nh : pl.nh * pl.epi_warps;
   p.limit_ns = d.wait_limit_us > 0 ? (unsigned long long)d.wait_limit_us * 1000ull : kDefaultWaitNs;
   p.ctl = reinterpret_cast<Control*>(ws);
