@@ -10,13 +10,16 @@
 //   backward), apply the gates with c carried in fp32 registers, and publish
 //   h[t+1] / c[t+1].  h is exchanged between the CTAs of a batch tile through
 //   global memory (L2): one arrival counter per (timestep, batch tile), released
-//   by every epilogue warp and acquired (bounded spin) by the TMA producer of each
-//   CTA before it streams h[t+1].  Each CTA interleaves up to two independent
-//   batch tiles so the hand-off latency of one hides behind the math of the other.
+//   by the epilogue warps (or, with interleaved tiles, by a publisher warp on their
+//   behalf) and acquired (bounded spin) by the TMA producer of each CTA before it
+//   streams h[t+1].  Each CTA interleaves up to four independent batch tiles so the
+//   hand-off latency of one hides behind the work of the others.
 //
-//   warp 0      TMA producer (flag wait, h tiles, Wh slice once)
-//   warp 1      tcgen05.mma issuer, TMEM owner
-//   warps 2..   epilogue: thread = batch row, 16 hidden units x 4 gates per thread
+//   warp 0        TMA producer (flag wait, h tiles, Wh slice once)
+//   warps 1..NACC tcgen05.mma issuers (each owns whole K chunks and its own TMEM
+//                 accumulator; warp 1 owns the TMEM allocation)
+//   next warp     publisher (interleaved tiles only): proxy fence + release per item
+//   last 4 or 8   epilogue: thread = batch row x 8 or 16 hidden units x 4 gates
 #include <stdlib.h>
 
 #include "generic.cuh"
@@ -583,7 +586,7 @@ static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensor
 // TMEM; the four partials are reduce-scattered through distributed shared memory (each CTA
 // receives the three 16-unit slices it needs, 24 KB per step) so that CTA r finishes with
 // dh for units [16r, 16r+16) of the cluster's 64 - the units whose gate maths it then
-// does (thread = batch row: dc carried in fp32 registers, d_ifgo[t-1] written and
+// does (thread = batch row x 8 units: dc carried in fp32 registers, d_ifgo[t-1] written and
 // published with the same per-(step, batch tile) arrival counters as the forward kernel).
 // =====================================================================================
 constexpr int DB_PARTS = 256;             // row groups of the bias-gradient column sum
