@@ -138,3 +138,49 @@ def test_backward_recurrence(dtype, shape):
     assert torch.allclose(got[3], got[0].float().sum(dim=(0, 1)), rtol=1e-4, atol=1e-3 * T * B ** 0.5)
     again = _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh)
     assert torch.equal(got[0], again[0]) and torch.equal(got[1], again[1]) and torch.equal(got[3], again[3])
+
+
+# One tile in flight (arrivals by the epilogue warps) and interleaved tiles (arrivals by the
+# publisher warp; for the backward kernel also the cluster exchange has to give up cleanly).
+@pytest.mark.parametrize("shape", [(4, 128, 64), (4, 1300, 512)])
+@pytest.mark.parametrize("phase", ["fwd", "bwd"])
+def test_tensor_core_kernels_give_up_with_a_status_when_nothing_arrives(phase, shape):
+    """Failure detection without a fault: with the test hook that suppresses every arrival the
+    bounded waits of the tcgen05 kernels run out (20 ms), every role leaves its loop, the kernel
+    returns, the control block holds BLSTM_E_WAIT_TIMEOUT, and the next ordinary launch works."""
+    import ctypes
+    lib = _lib.load()
+    T, B, H = shape
+    dt = torch.bfloat16
+    d = _lib.Desc(_lib.DTYPE_CODE["bf16"], T, B, H, H, _lib.FLAG_TEST_NO_ARRIVE, 20000, 0)
+    assert lib.blstm_plan_name(d, 0 if phase == "fwd" else 1) == b"sm100"
+    s = torch.cuda.current_stream().cuda_stream
+    z = lambda *shape_: torch.zeros(*shape_, device="cuda", dtype=dt)
+    Wh = z(4 * H, H)
+    detail = (ctypes.c_int32 * 2)()
+    if phase == "fwd":
+        n = lib.blstm_workspace_bytes(d, _lib.PHASE_FWD)
+        ws = torch.zeros(n, dtype=torch.uint8, device="cuda")
+        ifgo, out, cell = z(T, B, 4 * H), z(T + 1, B, H), z(T + 1, B, H)
+        assert lib.blstm_fwd_recurrence(d, ifgo.data_ptr(), Wh.data_ptr(), out.data_ptr(), cell.data_ptr(),
+                                        ws.data_ptr(), n, s) == 0
+    else:
+        n = lib.blstm_workspace_bytes(d, _lib.PHASE_BWD)
+        ws = torch.zeros(n, dtype=torch.uint8, device="cuda")
+        ifgo, cell, dout, dg = z(T, B, 4 * H), z(T + 1, B, H), z(T, B, H), z(T, B, 4 * H)
+        dh0, dc0 = z(B, H), z(B, H)
+        assert lib.blstm_bwd_recurrence(d, dout.data_ptr(), None, None, ifgo.data_ptr(), cell.data_ptr(),
+                                        Wh.data_ptr(), dg.data_ptr(), dh0.data_ptr(), dc0.data_ptr(), None,
+                                        ws.data_ptr(), n, s) == 0
+    assert lib.blstm_read_status(ws.data_ptr(), detail, s) == _lib.E_WAIT_TIMEOUT
+    # the context is intact: the same problem without the hook runs to completion
+    ok = _lib.Desc(_lib.DTYPE_CODE["bf16"], T, B, H, H, 0, 0, 0)
+    ws.zero_()
+    if phase == "fwd":
+        assert lib.blstm_fwd_recurrence(ok, ifgo.data_ptr(), Wh.data_ptr(), out.data_ptr(), cell.data_ptr(),
+                                        ws.data_ptr(), n, s) == 0
+    else:
+        assert lib.blstm_bwd_recurrence(ok, dout.data_ptr(), None, None, ifgo.data_ptr(), cell.data_ptr(),
+                                        Wh.data_ptr(), dg.data_ptr(), dh0.data_ptr(), dc0.data_ptr(), None,
+                                        ws.data_ptr(), n, s) == 0
+    assert lib.blstm_read_status(ws.data_ptr(), None, s) == 0
