@@ -108,7 +108,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // A thread needs ~150-300 clocks per cp.async.bulk.tensor issue, and the M/N-major operand forms
+    // need one box per 64-element chunk (up to six boxes per k-block, more than the k-block's MMAs
+    // take), so every box has its own lane: the lanes walk the stages in lockstep, lane 0 arms the
+    // stage's barrier, each lane issues one load.
+    constexpr int NA = A_MN ? 2 : 1, NB = B_MN ? 4 : 1;
+    if (lane < NA + NB) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -120,19 +125,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (!mbar_wait(&empty[s], ph ^ 1, wc)) { ok = false; break; }
           uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
-          mbar_expect_tx(&full[s], STAGE_BYTES);
+          if (lane == 0) mbar_expect_tx(&full[s], STAGE_BYTES);
           const int k0 = kb * BK;
-          if (A_MN) {
-            tma_load_2d(sa, &tmA, &full[s], m0, k0);
-            tma_load_2d(sa + 8192, &tmA, &full[s], m0 + 64, k0);
+          if (lane < NA) {
+            if (A_MN) tma_load_2d(sa + lane * 8192, &tmA, &full[s], m0 + 64 * lane, k0);
+            else      tma_load_2d(sa, &tmA, &full[s], k0, m0);
           } else {
-            tma_load_2d(sa, &tmA, &full[s], k0, m0);
-          }
-          if (B_MN) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[s], n0 + 64 * j, k0);
-          } else {
-            tma_load_2d(sb, &tmB, &full[s], k0, n0);
+            const int j = lane - NA;
+            if (B_MN) tma_load_2d(sb + j * 8192, &tmB, &full[s], n0 + 64 * j, k0);
+            else      tma_load_2d(sb, &tmB, &full[s], k0, n0);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
