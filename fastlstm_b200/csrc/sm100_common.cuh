@@ -85,6 +85,11 @@ __device__ __forceinline__ uint32_t smem_count_arrive(int* counter) {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t remote_bar_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
 }
+// The same without release semantics: a pure "go ahead" signal that publishes no data of this thread
+// (a release at cluster scope waits for the thread's outstanding memory operations, ~1 k clocks).
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t remote_bar_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

@@ -595,7 +595,7 @@ constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x
 
 struct BwdPlan {
   bool ok;
-  int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni, ws;
+  int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni, ws, alias;
   size_t w_bytes, recv_bytes, stage_bytes, smem;
   size_t off_flags, n_flags, off_db, ws_bytes;
 };
@@ -633,13 +633,26 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
     p.TI = 1;                                               // not enough room to interleave tiles
     p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
   }
-  const size_t fixed = 1024 + wres + p.recv_bytes + 384;    // 384: barriers and counters behind the ring
+  size_t fixed = 1024 + wres + p.recv_bytes + 384;          // 384: barriers and counters behind the ring
   // warps: 1 producer + 3 MMA issuers (or 2 + a publisher warp when tiles are interleaved) + 2 epilogue
   // warpgroups = 12 (3 per SM sub-partition, 168 registers each); a 13th warp would cap every thread
   // at 128 registers.
   const int n_issuers = p.TI >= 2 ? 2 : 3;
   p.threads = 32 * 12;
   if (!pick_ring(fixed, p.stage_bytes, n_issuers, H / RK, &p.stages, &p.ni)) return p;
+  // One tile in flight and a shallow ring (H = 768, 1024: the resident weights leave three stages):
+  // the ring is idle while an item's slices cross the cluster, so the exchange buffers are laid over
+  // its first stages and the ring gets their 48 KB.  A peer may then write a slice only after this
+  // CTA has finished the item's MMAs, which each CTA tells its peers (see `rdy` in the kernel).
+  p.alias = 0;
+  if (p.TI == 1 && p.stages < 6) {
+    int st2 = 0, ni2 = 0;
+    const size_t fixed2 = 1024 + wres + 384;
+    if (pick_ring(fixed2, p.stage_bytes, n_issuers, H / RK, &st2, &ni2) && st2 > p.stages &&
+        (size_t)st2 * p.stage_bytes >= p.recv_bytes) {
+      p.alias = 1; p.stages = st2; p.ni = ni2; fixed = fixed2;
+    }
+  }
   p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)d.seq_len * p.nbt;
   p.off_flags = sizeof(Control);
@@ -660,6 +673,7 @@ struct BwdParams {
   int no_arrive;
   int flag_target;          // arrivals that complete a flag: H/16 CTAs per batch tile [x 8 epilogue warps]
   int cta_publish;          // 1: one arrival per CTA and item, 0: one per epilogue warp
+  int alias;                // 1: exchange buffers laid over the first ring stages (one tile in flight)
   unsigned long long limit_ns;
   Control* ctl;
   int* flags;               // [T][nbt]: arrivals for d_ifgo[t]
@@ -711,7 +725,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint8_t* recv = smem + (p.ws ? 0 : (size_t)H * 128);                     // [XB][3 senders][128 rows][64 B]
   constexpr int XB = TI >= 2 ? 2 : 1;                         // exchange buffers (by item parity)
   uint8_t* stage = recv + (size_t)XB * 3 * XSLOT_BYTES;      // [XB][3 receivers][128 rows][64 B]
-  uint8_t* a_s = stage + (size_t)XB * 3 * XSLOT_BYTES;
+  uint8_t* a_s = p.alias ? recv : stage + (size_t)XB * 3 * XSLOT_BYTES;   // ring (over the exchange buffers if aliased)
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;
   uint64_t* empty = bars + R_MAX_STAGES;
@@ -724,6 +738,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* pub_cnt = const_cast<int*>(dead) + 1;        // [4] arrivals of the epilogue warps, by item index mod 4
   uint64_t* pub_bar = reinterpret_cast<uint64_t*>(pub_cnt + 4);   // [4] item published? by item index mod 4
+  uint64_t* rdy = pub_bar + 4;                                 // aliased buffers: the 3 peers are done with their MMAs
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t r = cluster_ctarank();                       // gate whose K range this CTA owns
@@ -742,6 +757,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     *dead = 0;
     for (int i = 0; i < 4; ++i) pub_cnt[i] = 0;
     for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], ITEM_WARPS);
+    mbar_init(rdy, 3);
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
@@ -999,6 +1015,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             wc.d0 = T - st; wc.d1 = bt;
             if (!mbar_wait(&acc_full[a], a_ph, wc)) { ok = false; break; }
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 3, (long long)clock64());
+            if (p.alias && shipper) {
+              // this item's MMAs are done (their reads of the ring completed before acc_full did), so
+              // the ring - and the exchange buffers laid over it - is idle until the next item: tell
+              // the three peers they may write their slices.  Nothing of this thread is published by
+              // the signal, hence relaxed.
+#pragma unroll
+              for (int dst = 0; dst < 4; ++dst)
+                if (dst != (int)r) mbar_arrive_remote_relaxed(mapa_shared(smem_u32(rdy), dst));
+            }
             tc_fence_after();
             RT2(0);
             const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16) + uoff;
@@ -1040,7 +1065,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             RT2(10);
             // one thread ships the three slices once all eight epilogue warps have staged their part
             // (bounded mbarrier wait, never a named barrier: a warp that gave up must not strand the rest)
-            if (shipper && mbar_wait(&staged[xb], x_ph, wc)) {
+            if (shipper && mbar_wait(&staged[xb], x_ph, wc) &&
+                (!p.alias || mbar_wait_cluster(rdy, x_ph, wc))) {   // aliased: every peer's ring is idle
               mbar_expect_tx(&xchg[xb], 3 * XSLOT_BYTES);      // what this CTA is about to receive
               RT2(11);
 #pragma unroll
@@ -1053,6 +1079,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                                   stage + ((size_t)xb * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES,
                                   XSLOT_BYTES, mapa_shared(smem_u32(&xchg[xb]), dst));
                 }
+              RT2(15);
             }
             if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 4, (long long)clock64());
             if (USE_FACTORS && !EARLY_FACTORS && st < T) factors();     // fills the wait for the peers' slices
@@ -1369,6 +1396,7 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   p.T = T; p.B = B; p.H = H;
   p.nbt = pl.nbt; p.nug = pl.nug; p.nb_par = pl.nb_par; p.ntl = pl.ntl; p.stages = pl.stages; p.ni = pl.ni;
   p.ws = pl.ws; p.stage_bytes = (int)pl.stage_bytes;
+  p.alias = pl.alias;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
   // Hundreds of same-address reductions per flag serialise in L2, while electing one publisher per
