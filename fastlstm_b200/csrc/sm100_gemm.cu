@@ -419,14 +419,28 @@ int gemm(int dtype, int M, int N, int K, const void* A, long long lda, bool a_mn
 }
 
 // ---------------------------------------------------------------- LSTM-level wrappers
+// Split-K factor of the weight-gradient GEMMs (K = T*B is long, the output has few tiles).  The grid is
+// persistent over tiles x splits work items, so what counts is how full the last wave of `sm_count`
+// CTAs is: take the smallest factor within 3 % of the best wave efficiency (every extra split adds an
+// fp32 partial of the output to write and reduce), with at least 8 k-blocks per split.
 static int pick_splits(int M, int N, int K, int sm_count) {
   const int tiles = cdiv(M, BM) * cdiv(N, BN);
-  if (tiles >= sm_count) return 1;
-  int s = sm_count / tiles;
   const int kb = cdiv(K, BK);
-  if (s > kb / 8) s = kb / 8;       // keep at least 8 k-blocks per split
-  if (s > 16) s = 16;
-  return s < 1 ? 1 : s;
+  int max_s = kb / 8;
+  if (max_s > 16) max_s = 16;
+  if (max_s < 1) max_s = 1;
+  double best = 0.0;
+  for (int s = 1; s <= max_s; ++s) {
+    const int items = tiles * s;
+    const double eff = (double)items / ((double)cdiv(items, sm_count) * sm_count);
+    if (eff > best) best = eff;
+  }
+  for (int s = 1; s <= max_s; ++s) {
+    const int items = tiles * s;
+    const double eff = (double)items / ((double)cdiv(items, sm_count) * sm_count);
+    if (eff >= best - 0.03) return s;
+  }
+  return 1;
 }
 
 }  // namespace sm100
