@@ -46,6 +46,7 @@ SIGNATURES = {
     "blstm_bwd_recurrence": (c_int, [DP, P, P, P, P, P, P, P, P, P, P, P, c_size_t, P]),
     "blstm_dgrad_input": (c_int, [DP, P, P, P, P, c_size_t, P]),
     "blstm_wgrad": (c_int, [DP, P, P, P, P, P, P, c_size_t, P]),
+    "blstm_bias_grad": (c_int, [DP, P, P, P, c_size_t, P]),
     "blstm_bwd": (c_int, [DP] + [P] * 17 + [c_size_t, P]),
     "blstm_read_status": (c_int, [P, POINTER(c_int32), P]),
     "blstm_launch_count": (ctypes.c_ulonglong, []),

@@ -47,6 +47,12 @@ int get_device_info(DeviceInfo* out) {
   return BLSTM_OK;
 }
 
+int plan_sm_count() {
+  DeviceInfo di;
+  if (get_device_info(&di) != BLSTM_OK || di.sm_count <= 0) return 148;
+  return di.sm_count;
+}
+
 static int check_desc(const blstm_desc* d) {
   if (!d) return BLSTM_E_INVALID_ARG;
   if (d->dtype != BLSTM_F32 && d->dtype != BLSTM_F16 && d->dtype != BLSTM_BF16) return BLSTM_E_INVALID_ARG;
@@ -224,6 +230,18 @@ int blstm_wgrad(const blstm_desc* d, const void* d_ifgo, const void* x, const vo
   rc = generic_gemm(d->dtype, true, G, I, TB, d_ifgo, 1, G, x, I, 1, dWx, I, nullptr, nullptr, st);
   if (rc) return rc;
   return generic_gemm(d->dtype, true, G, H, TB, d_ifgo, 1, G, out, H, 1, dWh, H, nullptr, nullptr, st);
+}
+
+int blstm_bias_grad(const blstm_desc* d, const void* d_ifgo, float* db, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  int rc = check_desc(d);
+  if (rc) return rc;
+  if (!d_ifgo || !db) return BLSTM_E_INVALID_ARG;
+  const BwdLayout L = bwd_layout(*d);
+  if (!ws_ok(workspace, workspace_bytes, L.rec_bytes)) return BLSTM_E_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (sm100_recurrence_supported(*d, BLSTM_PHASE_BWD)) return sm100_bias_grad(*d, d_ifgo, db, workspace, L.rec_bytes, st);
+  return generic_bias_grad(*d, d_ifgo, db, workspace, L.rec_bytes, st);
 }
 
 int blstm_bwd(const blstm_desc* d, const void* dout, const void* dh_n, const void* dc_n, const void* x,

@@ -142,5 +142,8 @@ struct DeviceInfo {
   size_t smem_optin;
 };
 int get_device_info(DeviceInfo* out);  // current device, cached per device
+// SM count the launch plans are sized for: the current device's, or 148 (a full B200) when no
+// device can be queried (workspace sizes asked for on a host without a GPU).
+int plan_sm_count();
 
 }  // namespace blstm

@@ -472,4 +472,34 @@ int generic_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh
   return BLSTM_OK;
 }
 
+// Column sums of d_ifgo [rows, cols]: part p adds the rows congruent to p modulo n_part, then
+// reduce_db adds the parts in a fixed order (deterministic).
+template <typename T>
+__global__ void gen_colsum_kernel(const T* __restrict__ g, int rows, int cols, int n_part, float* __restrict__ part) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= cols) return;
+  float s = 0.f;
+  for (int r = blockIdx.y; r < rows; r += n_part) s += ld_f(g + (size_t)r * cols + col);
+  part[(size_t)blockIdx.y * cols + col] = s;
+}
+
+int generic_bias_grad(const blstm_desc& d, const void* d_ifgo, float* db, void* ws, size_t ws_bytes,
+                      cudaStream_t st) {
+  GenericPlan pl;
+  pl.make(d, BLSTM_PHASE_BWD);
+  if (ws_bytes < pl.ws_bytes) return BLSTM_E_WORKSPACE;
+  float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + pl.off_db);
+  const int rows = d.seq_len * d.batch, cols = 4 * d.hidden_size;
+  dim3 grid(cdiv(cols, 128), pl.nbt);
+  switch (d.dtype) {
+    case BLSTM_F32: gen_colsum_kernel<float><<<grid, 128, 0, st>>>((const float*)d_ifgo, rows, cols, pl.nbt, part); break;
+    case BLSTM_F16: gen_colsum_kernel<__half><<<grid, 128, 0, st>>>((const __half*)d_ifgo, rows, cols, pl.nbt, part); break;
+    case BLSTM_BF16: gen_colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)d_ifgo, rows, cols, pl.nbt, part); break;
+    default: return BLSTM_E_INVALID_ARG;
+  }
+  BLSTM_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return reduce_db(part, pl.nbt, cols, db, st);
+}
+
 }  // namespace blstm

@@ -33,4 +33,8 @@ int generic_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh
 
 int reduce_db(const float* part, int n_part, int n, float* db, cudaStream_t st);
 
+// db[4H] = column sums of d_ifgo [T*B,4H]; scratch = the backward recurrence workspace of this plan
+int generic_bias_grad(const blstm_desc& d, const void* d_ifgo, float* db, void* ws, size_t ws_bytes,
+                      cudaStream_t st);
+
 }  // namespace blstm

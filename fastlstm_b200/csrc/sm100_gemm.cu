@@ -44,13 +44,6 @@ struct GemmParams {
   unsigned long long limit_ns;
 };
 
-#ifdef BLSTM_GEMM_TRACE
-__device__ long long g_trace[16384];
-#define TRACE(i, v) do { if (blockIdx.x == 0 && (i) < 16384) g_trace[(i)] = (v); } while (0)
-#else
-#define TRACE(i, v) do { } while (0)
-#endif
-
 template <typename T16>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
@@ -155,15 +148,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int z = tile / (p.n_tiles * p.m_tiles);
         const int kb0 = z * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
         const int a = it & 1;
-        TRACE(it * 8 + 0, (long long)globaltimer_ns());
         if (!mbar_wait(&acc_empty[a], acc_ph[a] ^ 1, wc)) { ok = false; break; }
         acc_ph[a] ^= 1;
-        TRACE(it * 8 + 1, (long long)globaltimer_ns());
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph, wc)) { ok = false; break; }
-          if (kb == kb0) TRACE(it * 8 + 2, (long long)globaltimer_ns());
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -176,7 +166,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit(&acc_full[a]);
-        TRACE(it * 8 + 3, (long long)globaltimer_ns());
       }
     }
   } else {
@@ -193,7 +182,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int a = it & 1;
       if (!mbar_wait(&acc_full[a], acc_ph[a], wc)) { ok = false; break; }
       acc_ph[a] ^= 1;
-      if (warp == 2 && lane == 0) TRACE(it * 8 + 4, (long long)globaltimer_ns());
       tc_fence_after();
       if (has_bias) {
         // bx + bh for this tile's 256 columns, rounded to the storage type (as the reference forms
@@ -270,7 +258,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[a]);
-      if (warp == 2 && lane == 0) TRACE(it * 8 + 5, (long long)globaltimer_ns());
     }
     if (lane == 0) tma_store_wait<0>();
   }
@@ -445,12 +432,6 @@ static int pick_splits(int M, int N, int K, int sm_count) {
 
 }  // namespace sm100
 
-#ifdef BLSTM_GEMM_TRACE
-extern "C" int blstm_dbg_trace(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, sm100::g_trace, sizeof(long long) * n);
-}
-#endif
-
 using namespace sm100;
 
 bool sm100_gemm_supported(const blstm_desc& d) {
@@ -461,7 +442,7 @@ bool sm100_gemm_supported(const blstm_desc& d) {
 }
 
 static int wgrad_splits(const blstm_desc& d, int N) {
-  return pick_splits(4 * d.hidden_size, N, d.seq_len * d.batch, 148);
+  return pick_splits(4 * d.hidden_size, N, d.seq_len * d.batch, plan_sm_count());
 }
 
 size_t sm100_bwd_gemm_workspace(const blstm_desc& d) {

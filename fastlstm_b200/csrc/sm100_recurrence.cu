@@ -34,15 +34,6 @@ constexpr int RK = 64;                  // K chunk (one 128-byte swizzle row)
 constexpr int R_MAX_STAGES = 8;
 constexpr int R_STAGE_BYTES = RB * RK * 2;   // 16 KB
 
-#ifdef BLSTM_REC_TRACE
-__device__ long long g_rtrace[16384];
-#define RTRACE(i, v) do { if (blockIdx.x == 0 && (i) < 16384) g_rtrace[(i)] = (v); } while (0)
-#define RT2(k) do { if (st == 100 && j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(8192 + 256 + (k), (long long)clock64()); } while (0)
-#else
-#define RTRACE(i, v) do { } while (0)
-#define RT2(k) do { } while (0)
-#endif
-
 // Ring depth R and number of concurrent TMA-issuing lanes / MMA-issuing warps NI.  Every stage
 // barrier must always be waited on by the SAME thread of each role (a parity wait cannot tell
 // phase n from phase n+2, so two threads sharing a barrier could lap each other): stage s belongs
@@ -77,7 +68,8 @@ struct RecPlan {
   size_t off_flags, n_flags, ws_bytes;
 };
 
-// Geometry is a pure function of the problem (no device query): 148 SMs assumed, the
+// Geometry follows the SM count of the current device (a B200 with all 148 SMs when no device can
+// be queried, e.g. when only a workspace size is asked for on a host without a GPU); the
 // cooperative launch refuses if the device cannot hold the grid.
 static RecPlan make_plan(const blstm_desc& d, int phase) {
   RecPlan p{};
@@ -93,8 +85,9 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.UH = UH;
   p.N = 4 * UH;
   p.nh = H / UH;
-  if (p.nh > 148) return p;
-  p.nb_par = 148 / p.nh;
+  const int sms = plan_sm_count();
+  if (p.nh > sms) return p;
+  p.nb_par = sms / p.nh;
   if (p.nb_par > p.nbt) p.nb_par = p.nbt;
   p.ntl = cdiv(p.nbt, p.nb_par);
   p.TI = p.ntl >= 3 ? 4 : p.ntl >= 2 ? 2 : 1;     // batch tiles interleaved per CTA (state: cell rows in registers)
@@ -273,7 +266,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (lane == 0) {
               wc.d0 = t; wc.d1 = bt;
               seen = wait_flag_ge(&p.flags[(size_t)t * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, t, bt) ? 1 : 0;
-              RTRACE(t * 8 + 0, (long long)clock64());
             }
             seen = __shfl_sync(0xffffffffu, seen, 0);
             if (!seen) { *dead = 1; ok = false; break; }
@@ -282,7 +274,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             // (cheaper there).  With interleaved tiles neither the epilogue warps nor this warp can afford
             // it (this loop then streams h without a break): the writers' publisher warp runs it.
             if (!WRITER_FENCE && !PUBLISHER) fence_proxy_async();
-            if (lane == 0) RTRACE(t * 8 + 1, (long long)clock64());
           }
           const int row0 = bt * RB;
           bool lane_ok = true;
@@ -295,7 +286,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               if (!mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
               tma_load_3d(a_s + (size_t)s * SB, &tmH, &full[s], kc * RK, row0, t);
               if (p.ws) tma_load_3d(a_s + (size_t)s * SB + R_STAGE_BYTES, &tmW, &full[s], kc * RK, ht * UH, 0);
-              if (t == 100) RTRACE(8192 + 64 + kc, (long long)clock64());
             }
           }
           if (__any_sync(0xffffffffu, !lane_ok)) { ok = false; break; }
@@ -361,8 +351,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait_spin(&full[s], ph, wc)) { ok = false; break; }
               mbar_expect_tx(&full[s], SB);   // arm the stage's next use
-              if (kc == 0) RTRACE(t * 8 + 2, (long long)clock64());
-              if (t == 100) RTRACE(8192 + kc * 2, (long long)clock64());
               tc_fence_after();
               const uint32_t sa = smem_u32(a_s + (size_t)s * SB);
               const uint32_t sb = p.ws ? sa + R_STAGE_BYTES : w_addr + (uint32_t)kc * N * 128;
@@ -372,10 +360,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                          (k > 0) ? 1u : acc_on);
               acc_on = 1;
               umma_commit(&empty[s]);
-              if (t == 100) RTRACE(8192 + kc * 2 + 1, (long long)clock64());
             }
             if (ok) umma_commit(&acc_full[a]);
-            if (x == 0) RTRACE(t * 8 + 3, (long long)clock64());
             gs += KC;
             while (gs >= R_STAGES) { gs -= R_STAGES; gph ^= 1; }
           }
@@ -434,7 +420,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           const bool row_ok = row < p.B;
           wc.d0 = t; wc.d1 = bt;
           if (!mbar_wait(&acc_full[a], a_ph, wc)) { ok = false; break; }
-          if (ew == 0 && lane == 0) RTRACE(t * 8 + 4, (long long)clock64());
           tc_fence_after();
           const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16) + ug * NU;
           // The thread's NU units are worked in passes of PW: accumulator read-out (the issuers' partial
@@ -472,7 +457,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(&acc_empty[a]);
-              if (ew == 0 && lane == 0) RTRACE(t * 8 + 5, (long long)clock64());
             }
 #pragma unroll
             for (int g = 0; g < 4; ++g)
@@ -506,7 +490,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           // publish h[t+1] first (it is all the peers wait for): generic-proxy stores -> proxy fence
           // (here or on the reading side) -> warp-level arrival with release semantics; peers read
           // the rows through TMA
-          if (ew == 0 && lane == 0) RTRACE(t * 8 + 6, (long long)clock64());
           if (WRITER_FENCE) fence_proxy_async();
           __syncwarp();
           // arrival per warp, or (cta_publish) one per CTA and item: the last epilogue warp to get here
@@ -520,7 +503,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               if (pub && !p.no_arrive) red_release_gpu_add(&p.flags[(size_t)(t + 1) * p.nbt + bt], 1);
             }
           }
-          if (ew == 0 && lane == 0) RTRACE(t * 8 + 7, (long long)clock64());
           // only now (after the release: a fence would otherwise wait for these loads) fetch the NEXT
           // item's projected pre-activations; they land while the peers run their step
           {
@@ -610,8 +592,9 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.nbt = cdiv(B, RB);
   p.nug = H / 64;
   const int per_tile = p.nug * 4;
-  if (per_tile > 148) return p;
-  p.nb_par = 148 / per_tile;
+  const int sms = plan_sm_count();
+  if (per_tile > sms) return p;
+  p.nb_par = sms / per_tile;
   if (p.nb_par > p.nbt) p.nb_par = p.nbt;
   p.ntl = cdiv(p.nbt, p.nb_par);
   // Batch tiles interleaved per CTA.  Their only per-tile state is the carries in registers: the
@@ -795,7 +778,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           if (lane == 0) {
             wc.d0 = tg; wc.d1 = bt;
             seen = wait_flag_ge(&p.flags[(size_t)tg * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, tg, bt) ? 1 : 0;
-            if (j == 0) RTRACE(st * 8 + 0, (long long)clock64());
           }
           seen = __shfl_sync(0xffffffffu, seen, 0);
           if (!seen) { *dead = 1; ok = false; break; }
@@ -880,7 +862,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait_spin(&full[s], ph, wc)) { ok = false; break; }
               mbar_expect_tx(&full[s], SB);   // arm the stage's next use
-              if (kc == 0 && j == 0) RTRACE(st * 8 + 1, (long long)clock64());
               tc_fence_after();
               const uint32_t sa = smem_u32(a_s + (size_t)s * SB);
               const uint32_t sb = p.ws ? sa + R_STAGE_BYTES : w_addr + (uint32_t)kc * 8192;
@@ -892,7 +873,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               umma_commit(&empty[s]);
             }
             if (ok) umma_commit(&acc_full[a]);
-            if (j == 0 && x == 0) RTRACE(st * 8 + 2, (long long)clock64());
             gs += KC;
             while (gs >= R_STAGES) { gs -= R_STAGES; gph ^= 1; }
           }
@@ -1014,7 +994,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             ++it;
             wc.d0 = T - st; wc.d1 = bt;
             if (!mbar_wait(&acc_full[a], a_ph, wc)) { ok = false; break; }
-            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 3, (long long)clock64());
             if (p.alias && shipper) {
               // this item's MMAs are done (their reads of the ring completed before acc_full did), so
               // the ring - and the exchange buffers laid over it - is idle until the next item: tell
@@ -1025,7 +1004,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                 if (dst != (int)r) mbar_arrive_remote_relaxed(mapa_shared(smem_u32(rdy), dst));
             }
             tc_fence_after();
-            RT2(0);
             const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16) + uoff;
 #pragma unroll
             for (int dst = 0; dst < 4; ++dst) {
@@ -1034,7 +1012,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 #pragma unroll
               for (int xx = 0; xx < NACC; ++xx) tmem_ld_32x8(taddr + xx * N + dst * 16, v[xx]);
               tmem_ld_wait();
-              RT2(1 + dst * 2);
               float sum[NU];
 #pragma unroll
               for (int u = 0; u < NU; ++u) {
@@ -1055,20 +1032,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                   *reinterpret_cast<float4*>(sp + (((uoff >> 2) + c4) ^ swz) * 16) =
                       make_float4(sum[4 * c4], sum[4 * c4 + 1], sum[4 * c4 + 2], sum[4 * c4 + 3]);
               }
-              RT2(2 + dst * 2);
             }
             tc_fence_before();
             fence_proxy_async_smem();                 // staged slices -> visible to the bulk-copy engine
-            RT2(9);
             __syncwarp();
             if (lane == 0) { mbar_arrive(&acc_empty[a]); mbar_arrive(&staged[xb]); }
-            RT2(10);
             // one thread ships the three slices once all eight epilogue warps have staged their part
             // (bounded mbarrier wait, never a named barrier: a warp that gave up must not strand the rest)
             if (shipper && mbar_wait(&staged[xb], x_ph, wc) &&
                 (!p.alias || mbar_wait_cluster(rdy, x_ph, wc))) {   // aliased: every peer's ring is idle
               mbar_expect_tx(&xchg[xb], 3 * XSLOT_BYTES);      // what this CTA is about to receive
-              RT2(11);
 #pragma unroll
               for (int dst = 0; dst < 4; ++dst)
                 if (dst != (int)r) {
@@ -1079,12 +1052,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                                   stage + ((size_t)xb * 3 + (dst < (int)r ? dst : dst - 1)) * XSLOT_BYTES,
                                   XSLOT_BYTES, mapa_shared(smem_u32(&xchg[xb]), dst));
                 }
-              RT2(15);
             }
-            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 4, (long long)clock64());
             if (USE_FACTORS && !EARLY_FACTORS && st < T) factors();     // fills the wait for the peers' slices
             if (!mbar_wait_cluster(&xchg[xb], x_ph, wc)) { ok = false; break; }
-            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 5, (long long)clock64());
             const uint8_t* rv = recv + (size_t)xb * (3 * XSLOT_BYTES) + row_in_tile * XROW_BYTES;
 #pragma unroll
             for (int c4 = 0; c4 < NU / 4; ++c4) {
@@ -1106,7 +1076,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           if (st < T) {
             // ---- gate maths of step t for this thread's row and 8 units, two per packed word
             const int t = T - 1 - st;
-            RT2(12);
             uint32_t qi[4], qf[4], qg[4], qo[4];
             if constexpr (USE_FACTORS) {
               if (!EARLY_FACTORS && st == 0) factors();   // later items computed them during the exchange
@@ -1170,12 +1139,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               stg16(dstp + 2 * (size_t)H, make_uint4(qg[0], qg[1], qg[2], qg[3]));
               stg16(dstp + 3 * (size_t)H, make_uint4(qo[0], qo[1], qo[2], qo[3]));
             }
-            RT2(13);
             // publish d_ifgo[t] rows of this warp, then (after the release) fetch the next item's inputs
-            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 6, (long long)clock64());
             if (WRITER_FENCE) fence_proxy_async();
             __syncwarp();
-            RT2(14);
             // interleaved tiles: hand the item to the publisher warp.  One tile: arrival per warp, or
             // (cta_publish) one per CTA and item - the last epilogue warp to get here publishes for all
             // (a warp can be at most four items ahead of another - the maths-only items that open a
@@ -1190,7 +1156,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               }
             }
             ++pub_it;
-            if (j == 0 && warp == FIRST_EPI && lane == 0) RTRACE(st * 8 + 7, (long long)clock64());
             {
               int nj = j + 1, ns = st;
               if (nj == TI || pb + (ch * TI + nj) * p.nb_par >= p.nbt) { nj = 0; ns = st + 1; }
@@ -1281,9 +1246,12 @@ static int launch_bwd_t(const BwdPlan& pl, const CUtensorMap& tw, const CUtensor
   BLSTM_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg));
   if (max_clusters * 4 < pl.grid) return BLSTM_E_NOT_CORESIDENT;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tg, p);
-  if (e != cudaSuccess) {
+  if (cfg.numAttrs == 2 && (e == cudaErrorNotSupported || e == cudaErrorCooperativeLaunchTooLarge)) {
+    // Only when the driver refuses the cooperative + cluster combination as such is the cooperative
+    // attribute dropped (co-residency then rests on the occupancy check above); any other launch error
+    // is reported as it is.
     (void)cudaGetLastError();
-    cfg.numAttrs = 1;   // cooperative + cluster refused: the occupancy check above already proved co-residency
+    cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, kern, tw, tg, p);
   }
   BLSTM_CUDA_OK(e);
@@ -1292,12 +1260,6 @@ static int launch_bwd_t(const BwdPlan& pl, const CUtensorMap& tw, const CUtensor
 }
 
 }  // namespace sm100
-
-#ifdef BLSTM_REC_TRACE
-extern "C" int blstm_dbg_rtrace(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, sm100::g_rtrace, sizeof(long long) * n);
-}
-#endif
 
 using namespace sm100;
 
@@ -1414,17 +1376,22 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   else if (pl.TI == 2) rc = bf ? launch_bwd_t<2, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<2, __half>(pl, tw, tg, p, st);
   else                 rc = bf ? launch_bwd_t<4, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<4, __half>(pl, tw, tg, p, st);
   if (rc) return rc;
-  if (db) {
-    float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + pl.off_db);
-    const int rows = T * B, cols = 4 * H;
-    dim3 grid(cdiv(cols, 1024), DB_PARTS);
-    if (bf) colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)d_ifgo, rows, cols, part);
-    else    colsum_kernel<__half><<<grid, 128, 0, st>>>((const __half*)d_ifgo, rows, cols, part);
-    BLSTM_CUDA_OK(cudaGetLastError());
-    count_launch();
-    return reduce_db(part, DB_PARTS, cols, db, st);
-  }
+  if (db) return sm100_bias_grad(d, d_ifgo, db, ws, ws_bytes, st);
   return BLSTM_OK;
+}
+
+int sm100_bias_grad(const blstm_desc& d, const void* d_ifgo, float* db, void* ws, size_t ws_bytes, cudaStream_t st) {
+  const BwdPlan pl = make_bwd_plan(d);
+  if (!pl.ok) return BLSTM_E_UNSUPPORTED;
+  if (ws_bytes < pl.ws_bytes) return BLSTM_E_WORKSPACE;
+  float* part = reinterpret_cast<float*>(static_cast<char*>(ws) + pl.off_db);
+  const int rows = d.seq_len * d.batch, cols = 4 * d.hidden_size;
+  dim3 grid(cdiv(cols, 1024), DB_PARTS);
+  if (d.dtype == BLSTM_BF16) colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)d_ifgo, rows, cols, part);
+  else                       colsum_kernel<__half><<<grid, 128, 0, st>>>((const __half*)d_ifgo, rows, cols, part);
+  BLSTM_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return reduce_db(part, DB_PARTS, cols, db, st);
 }
 
 }  // namespace blstm

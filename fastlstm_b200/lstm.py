@@ -169,11 +169,13 @@ def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh, inference=False):
     return out, cell, ifgo
 
 
-def lstm_persistent_bwd(dh, dc_n, dh_n, x, h, cell, ifgo, Wx, Wh, need_dx=True):
+def lstm_persistent_bwd(dh, dc_n, dh_n, x, h, cell, ifgo, Wx, Wh, need_dx=True, wgrads=None):
     """Backward of one layer.  dh [T,B,H] gradient of out[1:]; dc_n, dh_n [B,H]
     (or None) gradients of the final states; h = out[T+1,B,H] from forward.
     Returns (d_x, dh_0, dc_0, dWx, dbx, dWh, dbh); weight and bias gradients are
-    fp32, dbx is dbh.  (fastlstm/lstm.py:236-334)"""
+    fp32, dbx is dbh.  (fastlstm/lstm.py:236-334)
+    wgrads: optional flat fp32 tensor of 4H*(I+H+1) elements laid out dWx | dWh | db that the
+    kernels write into (a data-parallel gradient bucket); allocated here when None."""
     lib = _lib.load()
     T, B, H = dh.shape
     I = x.shape[-1]
@@ -191,7 +193,9 @@ def lstm_persistent_bwd(dh, dc_n, dh_n, x, h, cell, ifgo, Wx, Wh, need_dx=True):
         d_x = torch.empty((T, B, I), device=dev, dtype=dt) if need_dx else None
         carries = torch.empty((2, B, H), device=dev, dtype=dt)
         dh_0, dc_0 = carries.unbind(0)
-        wgrads = torch.empty(4 * H * (I + H + 1), device=dev, dtype=torch.float32)
+        if wgrads is None:
+            wgrads = torch.empty(4 * H * (I + H + 1), device=dev, dtype=torch.float32)
+        _require(wgrads, "wgrads", torch.float32, (4 * H * (I + H + 1),), dev)
         dWx = wgrads[:4 * H * I].view(4 * H, I)
         dWh = wgrads[4 * H * I:4 * H * (I + H)].view(4 * H, H)
         db = wgrads[4 * H * (I + H):]
@@ -221,7 +225,9 @@ def Wgrad(d_ifgo, x, h):
         rc = lib.blstm_wgrad(d, _ptr(d_ifgo), _ptr(x), _ptr(h), _ptr(dWx), _ptr(dWh), _ptr(ws),
                              ws_bytes, _stream(x))
         _lib.check(rc, "blstm_wgrad")
-        db = d_ifgo.reshape(T * B, G).sum(dim=0, dtype=torch.float32)
+        db = torch.empty(G, device=dev, dtype=torch.float32)
+        rc = lib.blstm_bias_grad(d, _ptr(d_ifgo), _ptr(db), _ptr(ws), ws_bytes, _stream(x))
+        _lib.check(rc, "blstm_bias_grad")
     return db, db, dWx, dWh
 
 
@@ -232,7 +238,7 @@ class PersistentLSTMfn(torch.autograd.Function):
     unlike the reference, h_n and c_n are flat outputs and differentiable."""
 
     @staticmethod
-    def forward(ctx, x, h_0, c_0, Wx, bx, Wh, bh):
+    def forward(ctx, x, h_0, c_0, Wx, bx, Wh, bh, inference=None, sink=None):
         if torch.is_autocast_enabled("cuda"):
             target = torch.get_autocast_dtype("cuda")
             x, Wx, Wh = x.to(target), Wx.to(target), Wh.to(target)
@@ -241,7 +247,14 @@ class PersistentLSTMfn(torch.autograd.Function):
             h_0 = None if h_0 is None else h_0.to(target)
             c_0 = None if c_0 is None else c_0.to(target)
         x = x.contiguous()
-        inference = not any(ctx.needs_input_grad)     # no_grad / nothing requires grad: save nothing
+        # Grad mode is always off inside Function.forward and needs_input_grad mirrors requires_grad
+        # whatever the grad mode, so the caller (persistent_lstm / FastLSTM.forward) decides whether
+        # anything has to be saved; a bare apply() with the reference's seven arguments saves unless
+        # no input requires a gradient.
+        if inference is None:
+            inference = not any(ctx.needs_input_grad)
+        ctx.inference = bool(inference)
+        ctx.sink = sink
         with torch.autograd.profiler.record_function("fastlstm_b200::fwd"):
             out, cell, ifgo = lstm_persistent_fwd(
                 x, None if h_0 is None else h_0.contiguous(), None if c_0 is None else c_0.contiguous(),
@@ -253,6 +266,8 @@ class PersistentLSTMfn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_out, d_hn, d_cn):
+        if ctx.inference:
+            raise RuntimeError("this forward ran in inference mode (nothing was saved); backward is not possible")
         x, out, cell, ifgo, Wx, Wh = ctx.saved_tensors
         T, B, H = out.shape[0] - 1, out.shape[1], out.shape[2]
         if d_out is None:
@@ -263,17 +278,28 @@ class PersistentLSTMfn(torch.autograd.Function):
         with torch.autograd.profiler.record_function("fastlstm_b200::bwd"):
             d_x, dh_0, dc_0, dWx, dbx, dWh, dbh = lstm_persistent_bwd(
                 d_out, d_cn, d_hn, x, out, cell, ifgo, Wx.contiguous(), Wh.contiguous(),
-                need_dx=ctx.needs_input_grad[0])
+                need_dx=ctx.needs_input_grad[0], wgrads=None if ctx.sink is None else ctx.sink.buffer)
         if ctx.h0_is_none:
             dh_0 = dc_0 = None
+        if ctx.sink is not None:
+            # the fp32 gradients went straight into the caller's bucket segment: autograd sees none
+            # (it would round them to the parameter dtype), the bucket hands them to p.grad later
+            ctx.sink.filled()
+            return (d_x, dh_0, dc_0, None, None, None, None, None, None)
         return (d_x, dh_0, dc_0, dWx, dbx if ctx.has_bias[0] else None, dWh,
-                dbh if ctx.has_bias[1] else None)
+                dbh if ctx.has_bias[1] else None, None, None)
+
+
+def _nothing_to_save(*tensors):
+    """True when no backward can follow this forward: grad mode is off, or no input requires one."""
+    return not (torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors))
 
 
 def persistent_lstm(x, h_0, c_0, Wx, bx, Wh, bh):
     """Reference-shaped call: returns (out, (h_n, c_n)) like PersistentLSTMfn.apply
     does in fastlstm/lstm.py:522."""
-    out, h_n, c_n = PersistentLSTMfn.apply(x, h_0, c_0, Wx, bx, Wh, bh)
+    inference = _nothing_to_save(x, h_0, c_0, Wx, bx, Wh, bh)
+    out, h_n, c_n = PersistentLSTMfn.apply(x, h_0, c_0, Wx, bx, Wh, bh, inference, None)
     return out, (h_n, c_n)
 
 
@@ -290,10 +316,15 @@ class FastLSTM(nn.Module):
     (states are ordered layer-major, direction-minor, like nn.LSTM); `dropout` is applied to
     the outputs of every layer but the last while training.  `proj_size` is not implemented."""
 
-    def __init__(self, input_size, hidden_size, num_layers=1, bias=True, batch_first=False,
+    def __init__(self, input_size, hidden_size, num_layers=1, *, bias=True, batch_first=False,
                  version="persistent", device=None, dtype=None, dropout=0.0, bidirectional=False,
                  proj_size=0):
+        # Everything after num_layers is keyword-only: the reference's positional order continues with
+        # (version, device, dtype), nn.LSTM's with (bias, batch_first, dropout, ...); a positional call
+        # written for either would silently bind the wrong option here, so it raises TypeError instead.
         super().__init__()
+        if not isinstance(bias, bool) or not isinstance(batch_first, bool):
+            raise TypeError("bias and batch_first must be bool")
         if version != "persistent":
             raise ValueError(f"Not implemented: {version} (only 'persistent' exists)")
         if proj_size != 0:
@@ -304,6 +335,7 @@ class FastLSTM(nn.Module):
         self.bias, self.batch_first, self.version = bias, batch_first, version
         self.dropout, self.bidirectional = float(dropout), bool(bidirectional)
         self.num_directions = 2 if bidirectional else 1
+        self._sinks = None            # per (layer, direction) gradient sinks of a GradBucket, or None
         k = 1.0 / hidden_size ** 0.5
         fk = dict(device=device, dtype=dtype)
 
@@ -348,7 +380,10 @@ class FastLSTM(nn.Module):
             for d in range(nd):
                 Wx, bx, Wh, bh = self.layer_params(layer, reverse=(d == 1))
                 x_d = x.flip(0) if d == 1 else x          # the reverse direction walks t = T-1 .. 0
-                o, h_i, c_i = PersistentLSTMfn.apply(x_d, h_0[layer * nd + d], c_0[layer * nd + d], Wx, bx, Wh, bh)
+                hl, cl = h_0[layer * nd + d], c_0[layer * nd + d]
+                inference = _nothing_to_save(x_d, hl, cl, Wx, bx, Wh, bh)
+                sink = None if self._sinks is None else self._sinks[layer * nd + d]
+                o, h_i, c_i = PersistentLSTMfn.apply(x_d, hl, cl, Wx, bx, Wh, bh, inference, sink)
                 outs.append(o.flip(0) if d == 1 else o)
                 h_n.append(h_i)
                 c_n.append(c_i)

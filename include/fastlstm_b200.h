@@ -139,6 +139,12 @@ int blstm_dgrad_input(const blstm_desc* d, const void* d_ifgo, const void* Wx, v
 int blstm_wgrad(const blstm_desc* d, const void* d_ifgo, const void* x, const void* out,
                 float* dWx, float* dWh, void* workspace, size_t workspace_bytes, void* stream);
 
+/* db[4H] (fp32) = sum over t,b of d_ifgo[T*B,4H]; `workspace` as for BLSTM_PHASE_BWD.
+ * Replaces `d_ifgo.sum(0)` of Wgrad, fastlstm/lstm.py:497 (blstm_bwd_recurrence already
+ * returns db; this entry serves callers that hold only d_ifgo). */
+int blstm_bias_grad(const blstm_desc* d, const void* d_ifgo, float* db, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
 /* Whole backward operator = bwd recurrence + dgrad + wgrad.  dx may be NULL
  * (input needs no gradient).  Replaces lstm_persistent_bwd, fastlstm/lstm.py:236-334. */
 int blstm_bwd(const blstm_desc* d, const void* dout, const void* dh_n, const void* dc_n,
