@@ -1,18 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the LSTM hot path (one JSON line on stdout, printed by rank 0).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1..c5] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1..c5] [--impl ours|reference|cudnn]
 
 A step is one forward+backward pass (forward only for c2) of the stacked LSTM
-over one batch of seeded synthetic input.  Workloads are the BASELINE configs;
+over one batch of seeded synthetic input.  Workloads c1..c5 are the five shapes listed in WORKLOADS;
 the default (c5: 2-layer bf16, global B=4096 split over the ranks, T=256,
 I=H=512, fwd+bwd, weight-gradient allreduce) is the one whose metric is quoted
 at 1/2/4/8 GPUs, so the same workload runs at every N (strong scaling).
 
   value     whole-job layer-tokens/s (L*B*T per step / time), inputs resident in HBM
   e2e       same metric through FastLSTM with pinned-host inputs copied in and the
-            final hidden state copied out inside the timed region
-  roofline  the persistent forward-recurrence kernel timed alone with CUDA events
+            step's results (the output sequence and the final hidden state) copied
+            back to pinned host memory inside the timed region
+  roofline  both persistent recurrence kernels timed alone with CUDA events; the
+            slower one is reported as the dominant kernel
+  cudnn     torch.nn.LSTM (cuDNN) on the same GPU, same dtype, same inputs and step
+            definition, weights flattened once; timed after the headline region
+            (1 GPU only).  `--impl cudnn` prints that arm as a line of its own.
   cpu_baseline / --impl reference
             torch.nn.LSTM fp32 on the host cores (the reference project's own CPU
             oracle), on a bounded batch sample of the same workload
@@ -88,6 +93,17 @@ class ClockSampler(threading.Thread):
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
+def workload_config(wl, cfg, world, seq_override=False):
+    """The keys that describe the workload; identical for every arm (ours, reference, cuDNN)."""
+    es = ESIZE[cfg["dtype"]]
+    B = cfg["B"]
+    return {"workload": wl if not seq_override else f"{wl} with T overridden to {cfg['T']} (profiling run, not the benchmark)",
+            "L": cfg["L"], "B": B, "B_per_gpu": B // world, "T": cfg["T"], "I": cfg["H"], "H": cfg["H"],
+            "pass": "fwd+bwd" if cfg["bwd"] else "fwd", "sharding": f"batch/{world}",
+            "l2": "inputs larger than L2 (no flush needed)" if (B // world) * cfg["T"] * cfg["H"] * es > 126e6
+                  else "inputs smaller than L2: L2 flushed (256 MB rewritten) before every timed step"}
+
+
 def cpu_baseline(wl, cfg, steps=1, warmup=1):
     """nn.LSTM fp32 on the host cores over a batch sample of the workload."""
     from oracle.torch_cpu import time_nn_lstm
@@ -117,12 +133,51 @@ def run_reference(args, wl, cfg):
         "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl, **{k: cfg[k] for k in ("L", "B", "T", "H")}, "cpu_sample_batch": min(CPU_SAMPLE_BATCH[wl], cfg["B"])},
+        "config": workload_config(wl, cfg, max(1, args.gpus), args.seq_len > 0),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
     }
     print(json.dumps(line), flush=True)
+
+
+def time_cudnn(cfg, dev, x_dev, dout, state, steps, warmup, autocast=False):
+    """ms per step of torch.nn.LSTM (cuDNN) on the same inputs.  Method of the reference's own
+    comparison (scripts/benchmark.py:43-68,118-133): same dtype, fwd or fwd+bwd, CUDA events after
+    warm-up; the weights are flattened once so no call compacts them.  autocast=True: fp32
+    parameters under torch.autocast (the variant the reference's README singles out for bf16)."""
+    import torch
+    dt = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[cfg["dtype"]]
+    torch.manual_seed(77)
+    m = torch.nn.LSTM(cfg["H"], cfg["H"], num_layers=cfg["L"], batch_first=cfg["batch_first"]).to(dev)
+    if not autocast:
+        m = m.to(dt)
+    m.flatten_parameters()
+    x = x_dev.detach().to(torch.float32 if autocast else dt).requires_grad_(cfg["bwd"])
+    st = None if state is None else tuple(t.to(x.dtype) for t in state)
+
+    def step():
+        if cfg["bwd"]:
+            for p in m.parameters():
+                p.grad = None
+            x.grad = None
+            with torch.autocast("cuda", dtype=dt, enabled=autocast):
+                out, _ = m(x, st)
+            out.backward(dout.to(out.dtype))
+        else:
+            with torch.no_grad(), torch.autocast("cuda", dtype=dt, enabled=autocast):
+                m(x, st)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
 
 
 def main():
@@ -131,8 +186,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "cudnn"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cudnn", action="store_true", help="skip the same-GPU torch.nn.LSTM (cuDNN) timing")
     ap.add_argument("--seq-len", type=int, default=0,
                     help="override T (profiling aid: shorter captures; the line then names the override)")
     args = ap.parse_args()
@@ -177,8 +233,36 @@ def main():
     if cfg["h0"] > 0:
         state = tuple((torch.randn(L, B, H, generator=gen) * cfg["h0"]).to(dt).to(dev) for _ in range(2))
     x_dev = x_host.to(dev).requires_grad_(cfg["bwd"])
-    hn_host = torch.empty((L, B, H), dtype=dt).pin_memory()
+    hn_host = torch.empty((L, B, H), dtype=dt, pin_memory=True)
+    out_host = torch.empty(shape, dtype=dt, pin_memory=True)
+    # data-parallel runs: every layer's backward writes its fp32 weight gradients straight into its
+    # segment of the bucket and starts that segment's allreduce; allreduce() waits and fills p.grad
     bucket = GradBucket(model) if (cfg["bwd"] and world > 1) else None
+    if bucket is not None:
+        bucket.attach()
+
+    if args.impl == "cudnn":
+        if world > 1:
+            if rank == 0:
+                print(json.dumps({"impl": "cudnn", "unavailable": "the cuDNN arm is a 1-GPU comparison"}), flush=True)
+            dist.barrier()
+            dist.destroy_process_group()
+            return
+        sampler = ClockSampler(local)
+        sampler.start()
+        ms = time_cudnn(cfg, dev, x_dev, dout, state, args.steps, args.warmup)
+        ms_ac = time_cudnn(cfg, dev, x_dev, dout, state, args.steps, args.warmup, autocast=True) if cfg["dtype"] != "fp32" else None
+        sampler.stop_flag = True
+        sampler.join(2)
+        print(json.dumps({
+            "impl": "cudnn", "metric": "fwd+bwd tokens/s per LSTM layer" if cfg["bwd"] else "fwd tokens/s per LSTM layer",
+            "value": L * Bg * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "ms_per_step_autocast": ms_ac, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
+            "config": workload_config(wl, cfg, 1, args.seq_len > 0),
+            "what": "torch.nn.LSTM (cuDNN), weights flattened",
+            "clocks": sampler.result()}), flush=True)
+        return
 
     def step(x):
         if cfg["bwd"]:
@@ -193,12 +277,13 @@ def main():
         else:
             with torch.no_grad():
                 out, (hn, cn) = model(x, state)
-        return hn
+        return out, hn
 
     # End-to-end input pipeline: every step's input is uploaded from pinned host memory into one of
     # two device buffers on a copy stream; the upload of step i+1 is issued before step i computes,
     # so it overlaps the kernels (one upload per step, all inside the timed region in steady state).
     copy_stream = torch.cuda.Stream(device=dev)
+    down_stream = torch.cuda.Stream(device=dev)           # results travel back beside the next step
     x_bufs = [torch.empty(shape, dtype=dt, device=dev) for _ in range(2)]
     uploaded = [torch.cuda.Event() for _ in range(2)]     # buffer k holds a fresh input
     consumed = [torch.cuda.Event() for _ in range(2)]     # the step that read buffer k has finished
@@ -217,8 +302,15 @@ def main():
         upload(k ^ 1)                                    # next step's input
         torch.cuda.current_stream().wait_event(uploaded[k])
         x = x_bufs[k].detach().requires_grad_(cfg["bwd"])
-        hn = step(x)
+        out, hn = step(x)
         consumed[k].record()
+        # the step's results go back to pinned host memory: the output sequence on a second copy
+        # stream (it overlaps the next step; the final synchronize of the timed region waits for it),
+        # the final hidden state on the compute stream
+        down_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(down_stream):
+            out_host.copy_(out.detach(), non_blocking=True)
+            out.record_stream(down_stream)
         hn_host.copy_(hn, non_blocking=True)
         pipe["i"] += 1
 
@@ -227,15 +319,33 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Workloads whose tensors fit the 126 MB L2 get the L2 flushed (a 256 MB buffer rewritten) before
+    # every timed step; each step then has its own event pair and the flush lies outside of it.
+    small = "smaller" in workload_config(wl, cfg, world)["l2"]
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
+
     def timed(fn, n):
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if flush_buf is None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            barrier()
+            total = e0.elapsed_time(e1)
+        else:
+            pairs = []
+            for _ in range(n):
+                flush_buf.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                pairs.append((e0, e1))
+            barrier()
+            total = sum(a.elapsed_time(b) for a, b in pairs)
+        ms = torch.tensor([total], device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
@@ -254,6 +364,14 @@ def main():
     sampler.stop_flag = True
     sampler.join(2)
     F.check_status()
+    cudnn = None
+    if world == 1 and not args.no_cudnn:
+        n_c = max(2, min(args.steps, 5))
+        c_ms = time_cudnn(cfg, dev, x_dev, dout, state, n_c, 3)
+        cudnn = {"ms_per_step": c_ms, "speedup": c_ms / (ms_total / args.steps),
+                 "what": "torch.nn.LSTM (cuDNN) same GPU, dtype, inputs and step; weights flattened; %d steps" % n_c}
+        if cfg["dtype"] != "fp32":
+            cudnn["ms_per_step_autocast"] = time_cudnn(cfg, dev, x_dev, dout, state, n_c, 3, autocast=True)
 
     tokens = L * Bg * T                      # layer-tokens per step, whole job
     ms_step = ms_total / args.steps
@@ -278,6 +396,8 @@ def main():
         for i in range(w + n):
             if prep:
                 prep()
+            if flush_buf is not None:
+                flush_buf.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()
@@ -339,22 +459,22 @@ def main():
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": cfg["dtype"], "data": "synthetic",
-        "config": {"workload": wl if not args.seq_len else f"{wl} with T overridden to {T} (profiling run, not the benchmark)",
-                   "L": L, "B": Bg, "B_per_gpu": B, "T": T, "I": H, "H": H,
-                   "pass": "fwd+bwd" if cfg["bwd"] else "fwd", "sharding": f"batch/{world}",
-                   "collective": "one fp32 sum-allreduce of dWx,dWh,db (NCCL)" if bucket is not None else "none",
-                   "l2": "inputs larger than L2 (no flush needed)" if x_host.numel() * es > 126e6 else "inputs smaller than L2; not flushed",
-                   "plan_fwd": lib.blstm_plan_name(d, 0).decode(), "plan_bwd": lib.blstm_plan_name(d, 1).decode()},
+        "config": workload_config(wl, cfg, world, args.seq_len > 0),
+        "collective": "fp32 sum-allreduce of dWx,dWh,db, one per layer, started from that layer's backward (NCCL)" if bucket is not None else "none",
+        "plans": {"fwd": F.plan_detail(dt, T, B, H, H, "fwd"), "bwd": F.plan_detail(dt, T, B, H, H, "bwd")},
         "us_per_timestep": ms_step * 1e3 / (T * L),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": x_host.numel() * es * world,
-                "d2h_bytes_per_step": hn_host.numel() * es * world,
-                "input_pipeline": "double-buffered upload on a copy stream, one upload per step"},
+                "d2h_bytes_per_step": (hn_host.numel() + out_host.numel()) * es * world,
+                "input_pipeline": "double-buffered upload on a copy stream, one upload per step; the output "
+                                  "sequence and h_n are copied back to pinned memory every step (gradients stay on the device)"},
         "gpu_launches": launches,
         "clocks": sampler.result(),
         "roofline": roof,
         "roofline_other_kernels": roof_other,
     }
+    if cudnn is not None:
+        line["cudnn"] = cudnn
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline(wl, cfg)

@@ -40,6 +40,7 @@ SIGNATURES = {
     "blstm_device_check": (c_int, [c_int]),
     "blstm_workspace_bytes": (c_size_t, [DP, c_int]),
     "blstm_plan_name": (c_char_p, [DP, c_int]),
+    "blstm_plan_detail": (c_int, [DP, c_int, ctypes.c_char_p, c_size_t]),
     "blstm_input_projection": (c_int, [DP, P, P, P, P, P, P]),
     "blstm_fwd_recurrence": (c_int, [DP, P, P, P, P, P, c_size_t, P]),
     "blstm_fwd": (c_int, [DP, P, P, P, P, P, P, P, P, P, P, P, c_size_t, P]),

@@ -140,6 +140,23 @@ const char* blstm_plan_name(const blstm_desc* d, int phase) {
   return sm100_recurrence_supported(*d, phase) ? "sm100" : "generic";
 }
 
+int blstm_plan_detail(const blstm_desc* d, int phase, char* buf, size_t buf_bytes) {
+  if (!buf || buf_bytes == 0) return BLSTM_E_INVALID_ARG;
+  buf[0] = 0;
+  int rc = check_desc(d);
+  if (rc) return rc;
+  if (sm100_recurrence_supported(*d, phase)) {
+    sm100_plan_detail(*d, phase, buf, buf_bytes);
+  } else {
+    GenericPlan pl;
+    pl.make(*d, phase);
+    snprintf(buf, buf_bytes, "generic %s rows_per_cta=%d units_per_cta=%d batch_tiles=%d hidden_tiles=%d wh=%s",
+             phase == BLSTM_PHASE_BWD ? "bwd" : "fwd", GenericPlan::kBT, GenericPlan::kUH, pl.nbt, pl.nh,
+             pl.w_in_smem ? "resident" : "global");
+  }
+  return BLSTM_OK;
+}
+
 int blstm_input_projection(const blstm_desc* d, const void* x, const void* Wx, const void* bx,
                            const void* bh, void* ifgo, void* stream) {
   int rc = check_desc(d);

@@ -25,6 +25,9 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
                          const void* ifgo, const void* cell, const void* Wh, void* d_ifgo, void* dh0,
                          void* dc0, float* db, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// one-line description of the launch plan of a phase ("" when the tcgen05 kernels do not cover it)
+int sm100_plan_detail(const blstm_desc& d, int phase, char* buf, size_t n);
+
 // db[4H] = column sums of d_ifgo [T*B,4H] (16-bit); scratch = the backward recurrence workspace
 int sm100_bias_grad(const blstm_desc& d, const void* d_ifgo, float* db, void* ws, size_t ws_bytes,
                     cudaStream_t st);

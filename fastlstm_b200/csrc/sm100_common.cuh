@@ -215,6 +215,19 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 // TMA store of one shared-memory box to global memory (bulk async-group completion).
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
@@ -313,11 +326,12 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt, int a_mn, int b_mn, i
 }
 
 // ---------------------------------------------------------------- host: tensor maps
-// Tiled map over a dense tensor of 2-byte (elem_bytes = 2) or 4-byte elements, 128-byte
-// swizzle, zero fill out of range.  dims/strides are given innermost first; strides (bytes)
+// Tiled map over a dense tensor of 2-byte (elem_bytes = 2) or 4-byte elements, zero fill out of range.  dims/strides are given innermost first; strides (bytes)
 // for dims 1.. only.
+// swizzle_bytes: 128 (default), 64, 32 or 0 (none): the shared-memory swizzle span of the boxes.
 int encode_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box, int elem_bytes = 2);
+                      const uint64_t* strides_bytes, const uint32_t* box, int elem_bytes = 2,
+                      int swizzle_bytes = 128);
 
 }  // namespace sm100
 }  // namespace blstm

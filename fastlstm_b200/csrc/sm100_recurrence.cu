@@ -20,6 +20,7 @@
 //                 accumulator; warp 1 owns the TMEM allocation)
 //   next warp     publisher (interleaved tiles only): proxy fence + release per item
 //   last 4 or 8   epilogue: thread = batch row x 8 or 16 hidden units x 4 gates
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "generic.cuh"
@@ -64,7 +65,8 @@ static bool pick_ring(size_t fixed_bytes, size_t stage_bytes, int max_ni, int kc
 struct RecPlan {
   bool ok;
   int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages, ni, ws;
-  size_t w_bytes, stage_bytes, smem;
+  int npb;                  // interleaved tiles: TMA landing buffers per epilogue warp (1 or 2), else 0
+  size_t w_bytes, stage_bytes, smem, ep_bytes;
   size_t off_flags, n_flags, ws_bytes;
 };
 
@@ -104,7 +106,21 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.w_bytes = (size_t)p.N * H * 2;
   p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;
   p.stage_bytes = R_STAGE_BYTES + (p.ws ? (size_t)p.N * 128 : 0);
-  const size_t fixed = 1024 + (p.ws ? 0 : p.w_bytes) + 256;
+  // Interleaved tiles: the epilogue's global traffic goes through TMA.  Every epilogue warp owns
+  // landing buffers for its 32 rows' projected pre-activations (4 gates x NU units; the final
+  // pre-activations are written back in place and stored from there) and one for the cell rows.
+  // Two landing buffers per warp (the next item's box is fetched a whole item ahead) when the ring
+  // still gets four stages, else one.
+  p.npb = 0;
+  p.ep_bytes = 0;
+  size_t fixed = 1024 + (p.ws ? 0 : p.w_bytes) + 512;
+  if (p.TI >= 2) {
+    const int NU = 4 * UH / p.epi_warps;
+    const size_t pb = 256 * (size_t)NU, cb = 64 * (size_t)NU;
+    p.npb = (fixed + p.epi_warps * (2 * pb + cb) + 4 * p.stage_bytes <= 232448) ? 2 : 1;
+    p.ep_bytes = p.epi_warps * (p.npb * pb + cb);
+    fixed += p.ep_bytes;
+  }
   if (!pick_ring(fixed, p.stage_bytes, n_issuers, H / RK, &p.stages, &p.ni)) return p;
   p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)(d.seq_len + 1) * p.nbt;
@@ -126,6 +142,8 @@ struct FwdParams {
   int inference;            // skip the stores that only backward needs
   int flag_target;          // arrivals that complete a flag: nh CTAs per batch tile [x epilogue warps]
   int cta_publish;          // 1: one arrival per CTA and item, 0: one per epilogue warp
+  int npb;                  // TMA landing buffers per epilogue warp (interleaved tiles)
+  int ep_bytes;             // bytes of the epilogue's TMA buffers (between the weights and the ring)
   unsigned long long limit_ns;
   Control* ctl;
   int* flags;
@@ -170,14 +188,39 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[NCOL]
   if constexpr (NCOL == 16) tmem_ld_32x16(taddr, r); else tmem_ld_32x8(taddr, r);
 }
 
+// Position in a CTA's sequence of work items, which every role walks in the same order:
+//   for chunk (TI tiles) : for step in [0, steps) : for j in [0, TI) : tile pb + (chunk*TI + j)*nb_par
+// (tiles past the last one are skipped).  next() moves to the following existing item.
+template <int TI>
+struct ItemCursor {
+  int ch, t, j;
+  __device__ __forceinline__ void init() { ch = 0; t = 0; j = -1; }
+  __device__ __forceinline__ bool next(int pb, int nb_par, int nbt, int n_chunks, int steps) {
+    for (;;) {
+      if (++j == TI) { j = 0; if (++t == steps) { t = 0; ++ch; } }
+      if (ch >= n_chunks) return false;
+      if (pb + (ch * TI + j) * nb_par < nbt) return true;
+    }
+  }
+  __device__ __forceinline__ int tile(int pb, int nb_par) const { return pb + (ch * TI + j) * nb_par; }
+};
+
 // UH: hidden units per CTA (16 or 32).  TI: batch tiles interleaved per CTA (1, 2 or 4).
 // Warps: 1 TMA producer, NACC MMA issuers, with interleaved tiles one publisher warp, 4 or 8 epilogue
 // warps - at most 12 (3 per SM sub-partition), which leaves 168 registers per thread; a 13th would cap
 // them at 128.  The epilogue must not spill.
 template <int UH, int TI, typename T16>
 __global__ void __launch_bounds__(32 * (UH == 16 && TI == 1 ? 9 : (TI >= 2 ? 12 : 11)), 1)
-fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmH, const FwdParams p) {
+fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmH,
+           const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmC, const FwdParams p) {
   constexpr int N = 4 * UH;
+  // Interleaved tiles are throughput bound, and there the epilogue's row-strided 16-byte global
+  // accesses (a thread owns a batch row: 32 sectors per warp instruction) were the bottleneck: the
+  // projected pre-activations come in, and the final pre-activations and cell rows go out, as TMA
+  // boxes through shared memory, one set of buffers per epilogue warp (tmP: ifgo as
+  // {unit, row, gate, step}, tmC: cell as {unit, row, step}).  Only h keeps its direct stores: they
+  // are what the step hand-off orders.
+  constexpr bool TMAEP = (TI >= 2);
   // Epilogue warps.  A single tile of 16 units is latency bound and runs best as one warpgroup with
   // 16 units per thread next to four issuers (9 warps); every other shape uses two warpgroups that
   // split the CTA's units (8 or 16 per thread), which keeps interleaved tiles free of spills.
@@ -192,7 +235,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint8_t* w_s = smem;                              // [KC][N rows][128 B]
   const int R_STAGES = p.stages;
   const int SB = p.stage_bytes;                     // h chunk (16 KB) [+ Wh chunk when streamed]
-  uint8_t* a_s = smem + (p.ws ? 0 : (size_t)N * H * 2);   // [stages][h chunk | optional Wh chunk]
+  uint8_t* ep_s = smem + (p.ws ? 0 : (size_t)N * H * 2);  // epilogue TMA buffers (interleaved tiles)
+  uint8_t* a_s = ep_s + p.ep_bytes;                       // [stages][h chunk | optional Wh chunk]
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;                            // [R_MAX_STAGES]
   uint64_t* empty = bars + R_MAX_STAGES;            // [R_MAX_STAGES]
@@ -203,6 +247,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* pub_cnt = const_cast<int*>(dead) + 1;        // [4] arrivals of the epilogue warps, by item index mod 4
   uint64_t* pub_bar = reinterpret_cast<uint64_t*>(pub_cnt + 4);   // [4] item stored? by item index mod 4
+  uint64_t* pre_full = pub_bar + 4;                 // [8 epilogue warps][2] landing buffer filled
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ht = blockIdx.x % p.nh, pb = blockIdx.x / p.nh;
@@ -228,10 +273,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     *dead = 0;
     for (int i = 0; i < 4; ++i) pub_cnt[i] = 0;
     for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], EW);
+    for (int i = 0; i < 16; ++i) mbar_init(&pre_full[i], 1);
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmH);
+    if (TMAEP) { tma_prefetch_desc(&tmP); tma_prefetch_desc(&tmC); }
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -368,6 +415,149 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
         }
       }
     }
+  } else if constexpr (TMAEP) {
+    // ---------------------------------------------------------------- epilogue, interleaved tiles
+    // thread = (batch row, NU units), worked in passes of 8 units.  Each warp owns `npb` landing
+    // buffers [4 gates][32 rows][NU units] and one cell buffer [32 rows][NU units]: rows of 16 bytes
+    // lie back to back, rows of 32 bytes carry the 32-byte swizzle, so the 32 lanes' 16-byte pieces of
+    // one gate fall into different banks.  Lane 0 issues the warp's TMA loads (`npb` items ahead) and
+    // stores.
+    constexpr int PB_BYTES = 256 * NU, CB_BYTES = 64 * NU, NPIECE = NU / 8;
+    const int ew = warp - FIRST_EPI;
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int ug = ew >> 2;
+    const int row_in_tile = q * 32 + lane;
+    const int unit0 = ht * UH + ug * NU;
+    const int npb = p.npb;
+    uint8_t* pbuf = ep_s + (size_t)ew * npb * PB_BYTES;
+    uint8_t* cbuf = ep_s + (size_t)EW * npb * PB_BYTES + (size_t)ew * CB_BYTES;
+    uint64_t* pfull = pre_full + 2 * ew;
+    T16* out = reinterpret_cast<T16*>(p.out);
+    const T16* cell = reinterpret_cast<const T16*>(p.cell);
+    auto c_off = [&](int v) { return (NU == 16) ? lane * 32 + ((v ^ ((lane >> 2) & 1)) * 16) : lane * 16; };
+    auto p_off = [&](int g, int v) { return g * (64 * NU) + c_off(v); };
+    // the load cursor runs `npb` items ahead of the item being worked on (lane 0 only)
+    ItemCursor<TI> lc;
+    lc.init();
+    bool lc_valid = lc.next(pb, p.nb_par, p.nbt, n_chunks, p.T);
+    int n_loaded = 0;
+    auto issue_load = [&]() {
+      if (!lc_valid) return;
+      const int b = (npb == 2) ? (n_loaded & 1) : 0;
+      mbar_expect_tx(&pfull[b], PB_BYTES);
+      tma_load_4d(pbuf + (size_t)b * PB_BYTES, &tmP, &pfull[b], unit0, lc.tile(pb, p.nb_par) * RB + q * 32, 0, lc.t);
+      ++n_loaded;
+      lc_valid = lc.next(pb, p.nb_par, p.nbt, n_chunks, p.T);
+    };
+    if (lane == 0)
+      for (int i = 0; i < npb; ++i) issue_load();
+    int it = 0;                             // items consumed
+    bool ok = true;
+    for (int ch = 0; ch < n_chunks && ok; ++ch) {
+      float c[TI][NU];
+#pragma unroll
+      for (int j = 0; j < TI; ++j) {
+        const int bt = pb + (ch * TI + j) * p.nb_par;
+        const int row = bt * RB + row_in_tile;
+#pragma unroll
+        for (int u = 0; u < NU; ++u) c[j][u] = 0.f;
+        if (bt < p.nbt && row < p.B) {
+#pragma unroll
+          for (int v = 0; v < NPIECE; ++v) unpack8<T16>(ldg16(cell + (size_t)row * H + unit0 + 8 * v), &c[j][8 * v]);
+        }
+      }
+      for (int t = 0; t < p.T && ok; ++t) {
+#pragma unroll
+        for (int j = 0; j < TI; ++j) {
+          const int bt = pb + (ch * TI + j) * p.nb_par;
+          if (bt >= p.nbt) continue;
+          const int a = it & 1;
+          const uint32_t a_ph = (uint32_t)(it >> 1) & 1u;
+          const int b = (npb == 2) ? (it & 1) : 0;
+          const uint32_t b_ph = (npb == 2) ? ((uint32_t)(it >> 1) & 1u) : ((uint32_t)it & 1u);
+          ++it;
+          const int row = bt * RB + row_in_tile;
+          const bool row_ok = row < p.B;
+          wc.d0 = t; wc.d1 = bt;
+          if (!mbar_wait(&acc_full[a], a_ph, wc)) { ok = false; break; }
+          if (!mbar_wait(&pfull[b], b_ph, wc)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t taddr = tmem_base + a * ACC_STRIDE + (uint32_t(q * 32) << 16) + ug * NU;
+          uint8_t* pbb = pbuf + (size_t)b * PB_BYTES;
+          const size_t o1 = ((size_t)(t + 1) * p.B + row) * H + unit0;
+#pragma unroll
+          for (int v = 0; v < NPIECE; ++v) {
+            float pa[4][8];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint32_t acc[NACC][8];
+#pragma unroll
+              for (int x = 0; x < NACC; ++x) tmem_ld_32x8(taddr + x * N + g * UH + 8 * v, acc[x]);
+              tmem_ld_wait();
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                float s0 = __uint_as_float(acc[0][u]);
+#pragma unroll
+                for (int x = 1; x < NACC; ++x)
+                  if (x < nacc) s0 += __uint_as_float(acc[x][u]);
+                pa[g][u] = s0;
+              }
+            }
+            if (v == NPIECE - 1) {
+              // the accumulator is in registers: hand the TMEM buffer back to the MMA warps
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[a]);
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint4 pw4 = *reinterpret_cast<const uint4*>(pbb + p_off(g, v));
+              const uint32_t w[4] = {pw4.x, pw4.y, pw4.z, pw4.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float2 f2 = cvt2<T16>(w[u]);
+                pa[g][2 * u] += f2.x;
+                pa[g][2 * u + 1] += f2.y;
+              }
+            }
+            float hv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const float cn = sigmoid_fast(pa[1][u]) * c[j][8 * v + u] + sigmoid_fast(pa[0][u]) * tanh_fast(pa[2][u]);
+              c[j][8 * v + u] = cn;
+              hv[u] = sigmoid_fast(pa[3][u]) * tanh_fast(cn);
+            }
+            if (row_ok) store8<T16>(out + o1 + 8 * v, hv);
+            // final pre-activations back in place, cell row into its buffer (16-bit, as stored)
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              *reinterpret_cast<uint4*>(pbb + p_off(g, v)) =
+                  make_uint4(pk2<T16>(pa[g][0], pa[g][1]), pk2<T16>(pa[g][2], pa[g][3]), pk2<T16>(pa[g][4], pa[g][5]),
+                             pk2<T16>(pa[g][6], pa[g][7]));
+            *reinterpret_cast<uint4*>(cbuf + c_off(v)) =
+                make_uint4(pk2<T16>(c[j][8 * v], c[j][8 * v + 1]), pk2<T16>(c[j][8 * v + 2], c[j][8 * v + 3]),
+                           pk2<T16>(c[j][8 * v + 4], c[j][8 * v + 5]), pk2<T16>(c[j][8 * v + 6], c[j][8 * v + 7]));
+          }
+          // publish h[t+1] first (it is all the peers wait for): the publisher warp fences and releases
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&pub_bar[(it - 1) & 3]);
+          // then hand the two boxes to TMA and, once they have been read out of shared memory, fetch
+          // the box of the item `npb` ahead into the landing buffer that just became free
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int row0 = bt * RB + q * 32;
+            if (!p.inference) tma_store_4d(&tmP, pbb, unit0, row0, 0, t);
+            if (!p.inference || t == p.T - 1) tma_store_3d(&tmC, cbuf, unit0, row0, t + 1);
+            tma_store_commit();
+            tma_store_wait_read<0>();
+            issue_load();
+          }
+          __syncwarp();
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
   } else {
     // ---------------------------------------------------------------- epilogue
     // thread = (batch row, NU units): warpgroup `ug` takes the ug-th group of NU of the CTA's UH units
@@ -547,11 +737,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 }
 
 template <int UH, int TI, typename T16>
-static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensorMap& th, FwdParams& p,
-                        cudaStream_t st) {
+static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensorMap& th, const CUtensorMap& tp,
+                        const CUtensorMap& tc, FwdParams& p, cudaStream_t st) {
   auto kern = fwd_kernel<UH, TI, T16>;
   BLSTM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-  void* args[] = {(void*)&tw, (void*)&th, (void*)&p};
+  void* args[] = {(void*)&tw, (void*)&th, (void*)&tp, (void*)&tc, (void*)&p};
   BLSTM_CUDA_OK(cudaLaunchCooperativeKernel((void*)kern, dim3(pl.grid), dim3(pl.threads), args, pl.smem, st));
   count_launch();
   return BLSTM_OK;
@@ -578,7 +768,7 @@ constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x
 struct BwdPlan {
   bool ok;
   int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni, ws, alias;
-  size_t w_bytes, recv_bytes, stage_bytes, smem;
+  size_t w_bytes, recv_bytes, stage_bytes, smem, ep_bytes;
   size_t off_flags, n_flags, off_db, ws_bytes;
 };
 
@@ -606,17 +796,18 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;                   // stream the Wh slice through the ring
   p.stage_bytes = R_STAGE_BYTES + (p.ws ? 8192 : 0);
   const size_t wres = p.ws ? 0 : p.w_bytes;
-  // Cluster exchange: receive slots (3 peers x 8 KB) and send staging (3 x 8 KB), each double
-  // buffered by item parity.  Every CTA of a cluster walks its items in the same order and waits for
-  // item n's slices before it stages item n+1, so slices of item n+2 cannot be sent (nor its staging
-  // reused) before item n has been consumed everywhere.  A single tile needs one buffer of each.
-  const int xbuf = p.TI >= 2 ? 2 : 1;
-  p.recv_bytes = (size_t)xbuf * 2 * 3 * XSLOT_BYTES;
-  if (1024 + wres + p.recv_bytes + 384 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
+  // Cluster exchange: receive slots (3 peers x 8 KB) and send staging (3 x 8 KB), one set.  With
+  // interleaved tiles a CTA tells its three peers when it has consumed an item's slices, and nobody
+  // stages or ships the next item before all three have said so (`consumed` in the kernel).
+  // Interleaved tiles also move the epilogue's gate traffic through TMA: two landing buffers per
+  // epilogue warp (32 rows x 4 gates x 8 units; d_ifgo is written back in place and stored from there).
+  p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
+  p.ep_bytes = p.TI >= 2 ? (size_t)8 * 2 * 2048 : 0;
+  if (1024 + wres + p.recv_bytes + p.ep_bytes + 512 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
     p.TI = 1;                                               // not enough room to interleave tiles
-    p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
+    p.ep_bytes = 0;
   }
-  size_t fixed = 1024 + wres + p.recv_bytes + 384;          // 384: barriers and counters behind the ring
+  size_t fixed = 1024 + wres + p.recv_bytes + p.ep_bytes + 512;   // 512: barriers and counters behind the ring
   // warps: 1 producer + 3 MMA issuers (or 2 + a publisher warp when tiles are interleaved) + 2 epilogue
   // warpgroups = 12 (3 per SM sub-partition, 168 registers each); a 13th warp would cap every thread
   // at 128 registers.
@@ -630,7 +821,7 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.alias = 0;
   if (p.TI == 1 && p.stages < 6) {
     int st2 = 0, ni2 = 0;
-    const size_t fixed2 = 1024 + wres + 384;
+    const size_t fixed2 = 1024 + wres + 512;
     if (pick_ring(fixed2, p.stage_bytes, n_issuers, H / RK, &st2, &ni2) && st2 > p.stages &&
         (size_t)st2 * p.stage_bytes >= p.recv_bytes) {
       p.alias = 1; p.stages = st2; p.ni = ni2; fixed = fixed2;
@@ -657,6 +848,7 @@ struct BwdParams {
   int flag_target;          // arrivals that complete a flag: H/16 CTAs per batch tile [x 8 epilogue warps]
   int cta_publish;          // 1: one arrival per CTA and item, 0: one per epilogue warp
   int alias;                // 1: exchange buffers laid over the first ring stages (one tile in flight)
+  int ep_bytes;             // bytes of the epilogue's TMA buffers (interleaved tiles)
   unsigned long long limit_ns;
   Control* ctl;
   int* flags;               // [T][nbt]: arrivals for d_ifgo[t]
@@ -687,7 +879,8 @@ __device__ __forceinline__ void store16(T16* dst, const float (&f)[16]) {
 
 template <int TI, typename T16>
 __global__ void __launch_bounds__(384, 1)
-bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG, const BwdParams p) {
+bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmG,
+           const __grid_constant__ CUtensorMap tmI, const __grid_constant__ CUtensorMap tmD, const BwdParams p) {
   // Warps: 0 = TMA producer, then NACC MMA issuers, then (interleaved tiles only) one PUBLISHER warp,
   // then 8 epilogue warps from warp 4 on - 12 in all either way.
   // With interleaved tiles the epilogue warps are the bottleneck, and the release that publishes an
@@ -698,6 +891,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   constexpr int FIRST_EPI = 4;
   constexpr bool WRITER_FENCE = (TI == 1);        // which side runs the generic->async proxy fence
   constexpr int ITEM_WARPS = 8;                   // epilogue warps, all working on every item
+  // Interleaved tiles are throughput bound and the epilogue's row-strided 16-byte global accesses were
+  // the bottleneck there: the saved pre-activations come in, and d_ifgo goes out, as TMA boxes through
+  // shared memory, one pair of landing buffers per epilogue warp (tmI: ifgo, tmD: d_ifgo, both
+  // as {unit, row, gate, step}).  The TMA store of d_ifgo[t] is also what the peers' producers read
+  // next, so a warp counts its item in only after its store has completed.
+  constexpr bool TMAEP = (TI >= 2);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int H = p.H;
@@ -705,10 +904,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   const int R_STAGES = p.stages;
   uint8_t* w_s = smem;                                        // [KC][64 k rows][128 B]
   const int SB = p.stage_bytes;                               // d_ifgo chunk (16 KB) [+ Wh chunk when streamed]
-  uint8_t* recv = smem + (p.ws ? 0 : (size_t)H * 128);                     // [XB][3 senders][128 rows][64 B]
-  constexpr int XB = TI >= 2 ? 2 : 1;                         // exchange buffers (by item parity)
-  uint8_t* stage = recv + (size_t)XB * 3 * XSLOT_BYTES;      // [XB][3 receivers][128 rows][64 B]
-  uint8_t* a_s = p.alias ? recv : stage + (size_t)XB * 3 * XSLOT_BYTES;   // ring (over the exchange buffers if aliased)
+  uint8_t* recv = smem + (p.ws ? 0 : (size_t)H * 128);                     // [3 senders][128 rows][64 B]
+  constexpr int XB = 1;                                       // one set of exchange buffers
+  uint8_t* stage = recv + (size_t)XB * 3 * XSLOT_BYTES;      // [3 receivers][128 rows][64 B]
+  uint8_t* ep_s = stage + (size_t)XB * 3 * XSLOT_BYTES;      // epilogue TMA buffers [8 warps][2][2 KB]
+  uint8_t* a_s = p.alias ? recv : ep_s + p.ep_bytes;         // ring (over the exchange buffers if aliased)
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;
   uint64_t* empty = bars + R_MAX_STAGES;
@@ -722,6 +922,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   int* pub_cnt = const_cast<int*>(dead) + 1;        // [4] arrivals of the epilogue warps, by item index mod 4
   uint64_t* pub_bar = reinterpret_cast<uint64_t*>(pub_cnt + 4);   // [4] item published? by item index mod 4
   uint64_t* rdy = pub_bar + 4;                                 // aliased buffers: the 3 peers are done with their MMAs
+  uint64_t* consumed = rdy + 1;                                // interleaved tiles: the 3 peers' 8 warps read an item's slices
+  uint64_t* pre_full = consumed + 1;                           // [8 epilogue warps][2] landing buffer filled
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t r = cluster_ctarank();                       // gate whose K range this CTA owns
@@ -741,10 +943,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int i = 0; i < 4; ++i) pub_cnt[i] = 0;
     for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], ITEM_WARPS);
     mbar_init(rdy, 3);
+    mbar_init(consumed, 3 * ITEM_WARPS);
+    for (int i = 0; i < 16; ++i) mbar_init(&pre_full[i], 1);
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmG);
+    if (TMAEP) { tma_prefetch_desc(&tmI); tma_prefetch_desc(&tmD); }
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -899,6 +1104,26 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     int it = 0;                 // MMA items consumed so far: TMEM buffer it & 1, on its (it >> 1)-th use
     int pub_it = 0;             // gate-maths items published so far
     bool ok = true;
+    // Interleaved tiles: this warp's two landing buffers [4 gates][32 rows][8 units] (16-byte rows back
+    // to back: the 32 lanes' pieces of one gate fall into different banks); lane 0 issues the warp's
+    // TMA loads two gate-maths items ahead, and its stores.
+    const int ew = warp - FIRST_EPI;
+    uint8_t* pbuf = ep_s + (size_t)ew * 2 * 2048;
+    uint64_t* pfull = pre_full + 2 * ew;
+    auto p_off = [&](int k) { return k * 512 + lane * 16; };
+    ItemCursor<TI> lc;
+    lc.init();
+    bool lc_valid = TMAEP && lc.next(pb, p.nb_par, p.nbt, n_chunks, T);
+    int n_loaded = 0;
+    auto issue_load = [&]() {
+      if (!lc_valid) return;
+      const int b = n_loaded & 1;
+      mbar_expect_tx(&pfull[b], 2048);
+      tma_load_4d(pbuf + b * 2048, &tmI, &pfull[b], unit0, lc.tile(pb, p.nb_par) * RB + q * 32, 0, T - 1 - lc.t);
+      ++n_loaded;
+      lc_valid = lc.next(pb, p.nb_par, p.nbt, n_chunks, T);
+    };
+    if (TMAEP && lane == 0) { issue_load(); issue_load(); }
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
       // dc is carried per interleaved tile; dh is rebuilt from the accumulator in every item, so one
       // copy serves all tiles (its first value, the gradient of h_n, is fetched in the tile's first item)
@@ -916,9 +1141,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       auto prefetch = [&](int t, int bt) {
         const int row = bt * RB + row_in_tile;
         if (bt < p.nbt && row < p.B) {
-          const T16* gsrc = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+          if constexpr (!TMAEP) {
+            const T16* gsrc = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) pf[k] = ldg16(gsrc + (size_t)k * H);
+            for (int k = 0; k < 4; ++k) pf[k] = ldg16(gsrc + (size_t)k * H);
+          }
           pf[4] = ldg16(cell + ((size_t)(t + 1) * p.B + row) * H + unit0);
           pf[5] = ldg16(cell + ((size_t)t * p.B + row) * H + unit0);
           pf[6] = ldg16(dout + ((size_t)t * p.B + row) * H + unit0);
@@ -929,9 +1156,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       auto prefetch_far = [&](int t, int bt) {
         const int row = bt * RB + row_in_tile;
         if (g == 0 && bt < p.nbt && row < p.B) {
-          const T16* gsrc = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
+          if constexpr (!TMAEP) {
+            const T16* gsrc = ifgo + ((size_t)t * p.B + row) * H4 + unit0;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) prefetch_l2(gsrc + (size_t)k * H);
+            for (int k = 0; k < 4; ++k) prefetch_l2(gsrc + (size_t)k * H);
+          }
           prefetch_l2(cell + ((size_t)t * p.B + row) * H + unit0);
           prefetch_l2(dout + ((size_t)t * p.B + row) * H + unit0);
         }
@@ -975,6 +1204,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
         }
         }
       };
+      // interleaved tiles: the gates of the item whose maths comes next, out of its landing buffer
+      auto fetch_gates = [&]() -> bool {
+        if constexpr (TMAEP) {
+          if (!mbar_wait(&pfull[pub_it & 1], (uint32_t)(pub_it >> 1) & 1u, wc)) return false;
+          const uint8_t* pbb = pbuf + (pub_it & 1) * 2048;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) pf[k] = *reinterpret_cast<const uint4*>(pbb + p_off(k));
+        }
+        return true;
+      };
       prefetch(T - 1, pb + (ch * TI) * p.nb_par);
       if (USE_FACTORS && EARLY_FACTORS) factors();
       for (int st = 0; st <= T && ok; ++st) {
@@ -988,12 +1227,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             // ---- dh = (sum over the cluster's four K ranges of) d_ifgo[T-st] x Wh
             const int a = it & 1;
             const uint32_t a_ph = (uint32_t)(it >> 1) & 1u;
-            // exchange buffers and their barriers go by item parity too (one set for a single tile)
-            const int xb = (XB == 2) ? a : 0;
-            const uint32_t x_ph = (XB == 2) ? a_ph : ((uint32_t)it & 1u);
+            // one set of exchange buffers: its barriers change phase with every item
+            constexpr int xb = 0;
+            const uint32_t x_ph = (uint32_t)it & 1u;
             ++it;
             wc.d0 = T - st; wc.d1 = bt;
             if (!mbar_wait(&acc_full[a], a_ph, wc)) { ok = false; break; }
+            if constexpr (TI >= 2) {
+              // the previous item's slices have been read by all three peers (so the staging below
+              // overwrites nothing a copy still reads, and the peers' receive slots are free again)
+              if (it > 1 && !mbar_wait_cluster(consumed, (uint32_t)it & 1u, wc)) { ok = false; break; }
+            }
             if (p.alias && shipper) {
               // this item's MMAs are done (their reads of the ring completed before acc_full did), so
               // the ring - and the exchange buffers laid over it - is idle until the next item: tell
@@ -1053,7 +1297,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                                   XSLOT_BYTES, mapa_shared(smem_u32(&xchg[xb]), dst));
                 }
             }
-            if (USE_FACTORS && !EARLY_FACTORS && st < T) factors();     // fills the wait for the peers' slices
+            if (USE_FACTORS && !EARLY_FACTORS && st < T) {               // fills the wait for the peers' slices
+              if (!fetch_gates()) { ok = false; break; }
+              factors();
+            }
             if (!mbar_wait_cluster(&xchg[xb], x_ph, wc)) { ok = false; break; }
             const uint8_t* rv = recv + (size_t)xb * (3 * XSLOT_BYTES) + row_in_tile * XROW_BYTES;
 #pragma unroll
@@ -1067,6 +1314,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               dhc[4 * c4 + 2] += s0.z + s1.z + s2.z;
               dhc[4 * c4 + 3] += s0.w + s1.w + s2.w;
             }
+            if constexpr (TI >= 2) {
+              // this warp has read the item's slices (the sums above hold them): tell the three peers.
+              // Nothing is published by the signal, hence relaxed.
+              __syncwarp();
+              if (lane == 0) {
+#pragma unroll
+                for (int dst = 0; dst < 4; ++dst)
+                  if (dst != (int)r) mbar_arrive_remote_relaxed(mapa_shared(smem_u32(consumed), dst));
+              }
+            }
           }
           if (st == 0) {
 #pragma unroll
@@ -1078,7 +1335,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             const int t = T - 1 - st;
             uint32_t qi[4], qf[4], qg[4], qo[4];
             if constexpr (USE_FACTORS) {
-              if (!EARLY_FACTORS && st == 0) factors();   // later items computed them during the exchange
+              if (!EARLY_FACTORS && st == 0) {            // later items computed them during the exchange
+                if (!fetch_gates()) { ok = false; break; }
+                factors();
+              }
 #pragma unroll
               for (int w = 0; w < 4; ++w) {
                 float r_[2][4];
@@ -1100,6 +1360,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               }
             } else {
               // four interleaved tiles leave no registers for the factors: all of the maths here
+              if (!fetch_gates()) { ok = false; break; }
               const uint32_t wi[4] = {pf[0].x, pf[0].y, pf[0].z, pf[0].w};
               const uint32_t wf[4] = {pf[1].x, pf[1].y, pf[1].z, pf[1].w};
               const uint32_t wg[4] = {pf[2].x, pf[2].y, pf[2].z, pf[2].w};
@@ -1132,7 +1393,25 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                 qo[w] = pk2<T16>(r_[0][3], r_[1][3]);
               }
             }
-            if (row_ok) {
+            if constexpr (TMAEP) {
+              // d_ifgo[t] goes back into the landing buffer the gates came from and leaves as one box;
+              // once it has been read out the buffer takes the gates of the item two ahead, and once it
+              // has been written (the peers' producers read it next) the warp counts the item in
+              uint8_t* pbb = pbuf + (pub_it & 1) * 2048;
+              *reinterpret_cast<uint4*>(pbb + p_off(0)) = make_uint4(qi[0], qi[1], qi[2], qi[3]);
+              *reinterpret_cast<uint4*>(pbb + p_off(1)) = make_uint4(qf[0], qf[1], qf[2], qf[3]);
+              *reinterpret_cast<uint4*>(pbb + p_off(2)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
+              *reinterpret_cast<uint4*>(pbb + p_off(3)) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_4d(&tmD, pbb, unit0, bt * RB + q * 32, 0, t);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+                issue_load();
+                tma_store_wait<0>();
+              }
+            } else if (row_ok) {
               T16* dstp = dg + ((size_t)t * p.B + row) * H4 + unit0;
               stg16(dstp, make_uint4(qi[0], qi[1], qi[2], qi[3]));
               stg16(dstp + (size_t)H, make_uint4(qf[0], qf[1], qf[2], qf[3]));
@@ -1221,7 +1500,8 @@ __global__ void __launch_bounds__(128) colsum_kernel(const T16* __restrict__ g, 
 }
 
 template <int TI, typename T16>
-static int launch_bwd_t(const BwdPlan& pl, const CUtensorMap& tw, const CUtensorMap& tg, BwdParams& p, cudaStream_t st) {
+static int launch_bwd_t(const BwdPlan& pl, const CUtensorMap& tw, const CUtensorMap& tg, const CUtensorMap& ti,
+                        const CUtensorMap& td, BwdParams& p, cudaStream_t st) {
   auto kern = bwd_kernel<TI, T16>;
   BLSTM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
   cudaLaunchConfig_t cfg = {};
@@ -1245,14 +1525,14 @@ static int launch_bwd_t(const BwdPlan& pl, const CUtensorMap& tw, const CUtensor
   int max_clusters = 0;
   BLSTM_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg));
   if (max_clusters * 4 < pl.grid) return BLSTM_E_NOT_CORESIDENT;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tg, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tg, ti, td, p);
   if (cfg.numAttrs == 2 && (e == cudaErrorNotSupported || e == cudaErrorCooperativeLaunchTooLarge)) {
     // Only when the driver refuses the cooperative + cluster combination as such is the cooperative
     // attribute dropped (co-residency then rests on the occupancy check above); any other launch error
     // is reported as it is.
     (void)cudaGetLastError();
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kern, tw, tg, p);
+    e = cudaLaunchKernelEx(&cfg, kern, tw, tg, ti, td, p);
   }
   BLSTM_CUDA_OK(e);
   count_launch();
@@ -1268,6 +1548,20 @@ bool sm100_recurrence_supported(const blstm_desc& d, int phase) {
 }
 size_t sm100_recurrence_workspace(const blstm_desc& d, int phase) {
   return phase == BLSTM_PHASE_BWD ? make_bwd_plan(d).ws_bytes : make_plan(d, phase).ws_bytes;
+}
+
+int sm100_plan_detail(const blstm_desc& d, int phase, char* buf, size_t n) {
+  if (phase == BLSTM_PHASE_BWD) {
+    const BwdPlan p = make_bwd_plan(d);
+    if (!p.ok) return 0;
+    return snprintf(buf, n, "sm100 bwd cluster=4 units_per_cluster=64 TI=%d grid=%d threads=%d stages=%d issuers=%d "
+                    "wh=%s alias=%d smem=%zu", p.TI, p.grid, p.threads, p.stages, p.ni,
+                    p.ws ? "streamed" : "resident", p.alias, p.smem);
+  }
+  const RecPlan p = make_plan(d, phase);
+  if (!p.ok) return 0;
+  return snprintf(buf, n, "sm100 fwd UH=%d TI=%d grid=%d threads=%d stages=%d issuers=%d wh=%s smem=%zu", p.UH, p.TI,
+                  p.grid, p.threads, p.stages, p.ni, p.ws ? "streamed" : "resident", p.smem);
 }
 
 int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* out, void* cell, void* ws,
@@ -1295,8 +1589,29 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
     rc = encode_tensor_map(&th, out, 3, dims, str, box);
     if (rc) return rc;
   }
+  CUtensorMap tp = th, tc = th;     // only read by the kernels that interleave tiles
+  if (pl.TI >= 2) {
+    const int NU = 4 * pl.UH / pl.epi_warps;
+    {  // ifgo [T,B,4H] as {unit, batch row, gate, t}: a box is one warp's 4 gates x 32 rows x NU units;
+       // the box's inner extent equals the swizzle span (32 bytes) or is a single 16-byte piece (none)
+      uint64_t dims[4] = {(uint64_t)H, (uint64_t)B, 4, (uint64_t)T};
+      uint64_t str[3] = {(uint64_t)4 * H * 2, (uint64_t)H * 2, (uint64_t)B * 4 * H * 2};
+      uint32_t box[4] = {(uint32_t)NU, 32, 4, 1};
+      rc = encode_tensor_map(&tp, ifgo, 4, dims, str, box, 2, NU == 16 ? 32 : 0);
+      if (rc) return rc;
+    }
+    {  // cell [T+1,B,H] as {unit, batch row, t}
+      uint64_t dims[3] = {(uint64_t)H, (uint64_t)B, (uint64_t)(T + 1)};
+      uint64_t str[2] = {(uint64_t)H * 2, (uint64_t)B * H * 2};
+      uint32_t box[3] = {(uint32_t)NU, 32, 1};
+      rc = encode_tensor_map(&tc, cell, 3, dims, str, box, 2, NU == 16 ? 32 : 0);
+      if (rc) return rc;
+    }
+  }
   BLSTM_CUDA_OK(cudaMemsetAsync(ws, 0, pl.ws_bytes, st));
   FwdParams p;
+  p.npb = pl.npb;
+  p.ep_bytes = (int)pl.ep_bytes;
   p.T = T; p.B = B; p.H = H;
   p.nbt = pl.nbt; p.nh = pl.nh; p.nb_par = pl.nb_par; p.ntl = pl.ntl;
   p.stages = pl.stages;
@@ -1317,7 +1632,8 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   const bool bf = d.dtype == BLSTM_BF16;
 #define BLSTM_FWD_CASE(U, I)                                                                         \
   if (pl.UH == U && pl.TI == I)                                                                      \
-    return bf ? launch_fwd_t<U, I, __nv_bfloat16>(pl, tw, th, p, st) : launch_fwd_t<U, I, __half>(pl, tw, th, p, st);
+    return bf ? launch_fwd_t<U, I, __nv_bfloat16>(pl, tw, th, tp, tc, p, st)                         \
+              : launch_fwd_t<U, I, __half>(pl, tw, th, tp, tc, p, st);
   BLSTM_FWD_CASE(16, 1)
   BLSTM_FWD_CASE(16, 2)
   BLSTM_FWD_CASE(16, 4)
@@ -1353,8 +1669,20 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
     rc = encode_tensor_map(&tg, d_ifgo, 3, dims, str, box);
     if (rc) return rc;
   }
+  CUtensorMap ti = tg, td = tg;     // only read by the kernels that interleave tiles
+  if (pl.TI >= 2) {
+    // ifgo and d_ifgo [T,B,4H] as {unit, batch row, gate, t}: a box is one warp's 4 gates x 32 rows x 8 units
+    uint64_t dims[4] = {(uint64_t)H, (uint64_t)B, 4, (uint64_t)T};
+    uint64_t str[3] = {(uint64_t)4 * H * 2, (uint64_t)H * 2, (uint64_t)B * 4 * H * 2};
+    uint32_t box[4] = {8, 32, 4, 1};
+    rc = encode_tensor_map(&ti, ifgo, 4, dims, str, box, 2, 0);
+    if (rc) return rc;
+    rc = encode_tensor_map(&td, d_ifgo, 4, dims, str, box, 2, 0);
+    if (rc) return rc;
+  }
   BLSTM_CUDA_OK(cudaMemsetAsync(ws, 0, pl.off_db, st));
   BwdParams p;
+  p.ep_bytes = (int)pl.ep_bytes;
   p.T = T; p.B = B; p.H = H;
   p.nbt = pl.nbt; p.nug = pl.nug; p.nb_par = pl.nb_par; p.ntl = pl.ntl; p.stages = pl.stages; p.ni = pl.ni;
   p.ws = pl.ws; p.stage_bytes = (int)pl.stage_bytes;
@@ -1372,9 +1700,9 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   p.dout = dout; p.dh_n = dh_n; p.dc_n = dc_n; p.ifgo = ifgo; p.cell = cell;
   p.d_ifgo = d_ifgo; p.dh0 = dh0; p.dc0 = dc0;
   const bool bf = d.dtype == BLSTM_BF16;
-  if (pl.TI == 1)      rc = bf ? launch_bwd_t<1, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<1, __half>(pl, tw, tg, p, st);
-  else if (pl.TI == 2) rc = bf ? launch_bwd_t<2, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<2, __half>(pl, tw, tg, p, st);
-  else                 rc = bf ? launch_bwd_t<4, __nv_bfloat16>(pl, tw, tg, p, st) : launch_bwd_t<4, __half>(pl, tw, tg, p, st);
+  if (pl.TI == 1)      rc = bf ? launch_bwd_t<1, __nv_bfloat16>(pl, tw, tg, ti, td, p, st) : launch_bwd_t<1, __half>(pl, tw, tg, ti, td, p, st);
+  else if (pl.TI == 2) rc = bf ? launch_bwd_t<2, __nv_bfloat16>(pl, tw, tg, ti, td, p, st) : launch_bwd_t<2, __half>(pl, tw, tg, ti, td, p, st);
+  else                 rc = bf ? launch_bwd_t<4, __nv_bfloat16>(pl, tw, tg, ti, td, p, st) : launch_bwd_t<4, __half>(pl, tw, tg, ti, td, p, st);
   if (rc) return rc;
   if (db) return sm100_bias_grad(d, d_ifgo, db, ws, ws_bytes, st);
   return BLSTM_OK;

@@ -131,6 +131,16 @@ def plan_name(dtype, T, B, I, H, phase="fwd"):
     return _lib.load().blstm_plan_name(d, _lib.PHASE_FWD if phase == "fwd" else _lib.PHASE_BWD).decode()
 
 
+def plan_detail(dtype, T, B, I, H, phase="fwd"):
+    """One-line description of the launch geometry the library picks for this problem."""
+    import ctypes
+    d = _desc(dtype, T, B, I, H)
+    buf = ctypes.create_string_buffer(512)
+    _lib.check(_lib.load().blstm_plan_detail(d, _lib.PHASE_FWD if phase == "fwd" else _lib.PHASE_BWD, buf, 512),
+               "blstm_plan_detail")
+    return buf.value.decode()
+
+
 # ---------------------------------------------------------------------------
 # Operator functions (same names and argument meaning as the reference)
 # ---------------------------------------------------------------------------

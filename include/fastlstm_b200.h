@@ -98,6 +98,12 @@ size_t blstm_workspace_bytes(const blstm_desc* d, int phase);
  * choice, fastlstm/configs.py:146-276 (prune_persistent_configs) and :29-58. */
 const char* blstm_plan_name(const blstm_desc* d, int phase);
 
+/* Writes a one-line, human-readable description of the launch geometry the phase will use
+ * (tile sizes, interleaved batch tiles, grid, ring depth) into the HOST buffer `buf`.
+ * Read-only; stands in for inspecting the reference's chosen autotune config
+ * (fastlstm/configs.py:146-276). */
+int blstm_plan_detail(const blstm_desc* d, int phase, char* buf, size_t buf_bytes);
+
 /* ifgo[T*B,4H] = x[T*B,I] * Wx^T + (bx + bh); bx/bh may be NULL.
  * Replaces torch.addmm at fastlstm/lstm.py:66-68. */
 int blstm_input_projection(const blstm_desc* d, const void* x, const void* Wx,

@@ -105,7 +105,7 @@ def norm_rel(got, ref):
 
 
 def assert_fp32_parity(res, ref, tol=1e-5, has_state=False):
-    """north-star fp32 bar: 1e-5 relative on outputs and gradients."""
+    """fp32 bar: 1e-5 relative (max-abs error / max-abs reference, per tensor) on outputs and gradients."""
     keys = ["out", "h_n", "c_n", "dx"] + (["dh0", "dc0"] if has_state else [])
     for k in keys:
         e = max_rel(res[k], ref[k])
@@ -119,7 +119,7 @@ def assert_fp32_parity(res, ref, tol=1e-5, has_state=False):
 
 
 def assert_half_parity(res, ref, has_state=False, abs_hc=2e-2, rel_w=5e-2):
-    """north-star 16-bit bar: 2e-2 absolute on h/c, 5e-2 relative on weight gradients
+    """16-bit bar: 2e-2 absolute on h/c, 5e-2 relative on weight gradients
     (norm-wise), against the fp32/fp64 oracle run on the same rounded inputs."""
     for k in ("out", "h_n", "c_n"):
         e = float(np.max(np.abs(res[k] - ref[k])))

@@ -1,4 +1,4 @@
-"""BASELINE configurations at their FULL sizes: CUDA path vs. torch.nn.LSTM fp32 on the host cores
+"""The five benchmark shapes at their FULL sizes: CUDA path vs. torch.nn.LSTM fp32 on the host cores
 (the reference's own oracle) on identical 16-bit-rounded inputs, plus size-independent properties
 where the CPU oracle would take too long (config 5)."""
 import numpy as np

@@ -69,7 +69,7 @@ def test_golden_batch_first_states_terminal_grads(golden_dir):
 
 # ---------------------------------------------------------------- fp32 vs oracle
 def test_config1_fp32_batch_first_full():
-    """BASELINE config 1: fp32, batch_first, B=16 T=64 I=H=128, terminal grads; 1e-5 rel."""
+    """Smallest benchmark shape: fp32, batch_first, B=16 T=64 I=H=128, terminal grads; 1e-5 rel."""
     case = make_case(1001, T=64, B=16, I=128, H=128, dtype="fp32", h0_std=0.1, terminal_grads=True)
     ref = run_oracle(case)
     res = run_module(case, batch_first=True)
@@ -123,7 +123,7 @@ def test_half_small_vs_oracle(dtype, shape):
 @pytest.mark.parametrize("dtype,T,B,H,L", [("fp16", 64, 64, 256, 1), ("fp16", 32, 256, 1024, 1),
                                            ("bf16", 32, 32, 2048, 1), ("bf16", 32, 256, 512, 2)])
 def test_half_baseline_shapes_short_sequence(dtype, T, B, H, L):
-    """The BASELINE hidden/batch sizes at a short T the oracle finishes in seconds."""
+    """The benchmark hidden/batch sizes at a short T the oracle finishes in seconds."""
     case = make_case(99 + H, T=T, B=B, I=H, H=H, L=L, dtype=dtype, h0_std=0.01)
     ref = run_oracle(case, np_dtype=np.float32)
     res = run_module(case)
@@ -180,9 +180,19 @@ def test_inference_mode_matches_training_forward():
         dt = TORCH_DT[dtype]
         x = case["x"].cuda().to(dt)
         st = (case["h0"].cuda().to(dt), case["c0"].cuda().to(dt))
-        y1, (h1, c1) = m(x.clone().requires_grad_(), st)
-        with torch.no_grad():
-            y2, (h2, c2) = m(x, st)
+        import fastlstm_b200.lstm as mod
+        seen = []
+        real = mod.lstm_persistent_fwd
+        mod.lstm_persistent_fwd = lambda *a, **k: (seen.append(k.get("inference")), real(*a, **k))[1]
+        try:
+            y1, (h1, c1) = m(x.clone().requires_grad_(), st)
+            assert seen == [False, False]               # trainable parameters, grad mode on: everything saved
+            del seen[:]
+            with torch.no_grad():
+                y2, (h2, c2) = m(x, st)
+            assert seen == [True, True], seen           # no_grad: the inference flag really reaches the kernels
+        finally:
+            mod.lstm_persistent_fwd = real
         assert torch.equal(y1, y2) and torch.equal(h1, h2) and torch.equal(c1, c2)
 
 

@@ -113,6 +113,31 @@ def _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh):
     return dg, dh0, dc0, db
 
 
+def _torch_bwd(dout, dh_n, dc_n, ifgo, cell, Wh):
+    """fp32 evaluation of the reverse recurrence, independent of both CUDA kernels: d_ifgo[t] is
+    rounded to the storage type before it feeds dh[t-1] = d_ifgo[t] x Wh (the kernels read it back
+    at storage precision); the dh and dc carries stay fp32.  Equations: fastlstm/kernels.py:1291-1316
+    and :1362-1383."""
+    T, B, G = ifgo.shape
+    H = G // 4
+    dt = ifgo.dtype
+    W = Wh.float()
+    dh_c, dc = dh_n.float(), dc_n.float()
+    dgs = [None] * T
+    for t in reversed(range(T)):
+        pi, pf, pg, po = ifgo[t].float().split(H, dim=1)
+        si, sf, so, tg = torch.sigmoid(pi), torch.sigmoid(pf), torch.sigmoid(po), torch.tanh(pg)
+        tc = torch.tanh(cell[t + 1].float())
+        dh = dout[t].float() + dh_c
+        dcv = dc + dh * so * (1 - tc * tc)
+        d = torch.cat([dcv * tg * si * (1 - si), dcv * cell[t].float() * sf * (1 - sf),
+                       dcv * si * (1 - tg * tg), dh * tc * so * (1 - so)], dim=1).to(dt)
+        dgs[t] = d
+        dc = dcv * sf
+        dh_c = d.float() @ W
+    return torch.stack(dgs), dh_c, dc
+
+
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("shape", BWD_SHAPES)
 def test_backward_recurrence(dtype, shape):
@@ -136,6 +161,11 @@ def test_backward_recurrence(dtype, shape):
     _cmp("dh0", got[1][None], ref[1][None], tol * max(float(ref[1].float().abs().max()), 1.0))
     _cmp("dc0", got[2][None], ref[2][None], tol * max(float(ref[2].float().abs().max()), 1.0))
     assert torch.allclose(got[3], got[0].float().sum(dim=(0, 1)), rtol=1e-4, atol=1e-3 * T * B ** 0.5)
+    # and against independent fp32 maths (not only the library's other kernel)
+    rg, rh, rc = _torch_bwd(dout, dh_n, dc_n, ifgo, cell, Wh)
+    _cmp("d_ifgo vs fp32 maths", got[0], rg, tol * max(float(rg.float().abs().max()), 1.0))
+    _cmp("dh0 vs fp32 maths", got[1][None], rh[None], tol * max(float(rh.abs().max()), 1.0))
+    _cmp("dc0 vs fp32 maths", got[2][None], rc[None], tol * max(float(rc.abs().max()), 1.0))
     again = _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh)
     assert torch.equal(got[0], again[0]) and torch.equal(got[1], again[1]) and torch.equal(got[3], again[3])
 
@@ -184,3 +214,32 @@ def test_tensor_core_kernels_give_up_with_a_status_when_nothing_arrives(phase, s
                                         Wh.data_ptr(), dg.data_ptr(), dh0.data_ptr(), dc0.data_ptr(), None,
                                         ws.data_ptr(), n, s) == 0
     assert lib.blstm_read_status(ws.data_ptr(), None, s) == 0
+
+
+# generic fp32; tcgen05 with one tile in flight, two and four interleaved tiles (16 units per CTA) and
+# 32 units per CTA with two interleaved tiles
+INFERENCE_CASES = [("fp32", 5, 40, 48), ("bf16", 6, 128, 256), ("fp16", 5, 2304, 256), ("bf16", 4, 1280, 1024),
+                   ("bf16", 6, 1300, 512)]
+
+
+@pytest.mark.parametrize("case", INFERENCE_CASES)
+def test_inference_flag_leaves_outputs_bit_identical(case):
+    """BLSTM_FLAG_INFERENCE skips the stores only backward needs: out[1..T] and cell[T] must be
+    bit-identical to a training-mode launch, and the saved tensors must really stay unwritten."""
+    lib = _lib.load()
+    dtype, T, B, H = case
+    dt = {"fp32": torch.float32, **TD}[dtype]
+    g = torch.Generator(device="cuda").manual_seed(T * B + H)
+    pre = torch.randn(T, B, 4 * H, generator=g, device="cuda").to(dt)
+    Wh = ((torch.rand(4 * H, H, generator=g, device="cuda") * 2 - 1) / H ** 0.5).to(dt)
+    h0 = (torch.randn(B, H, generator=g, device="cuda") * 0.3).to(dt)
+    c0 = (torch.randn(B, H, generator=g, device="cuda") * 0.3).to(dt)
+    train = _desc(dtype, T, B, H)
+    infer = _desc(dtype, T, B, H, _lib.FLAG_INFERENCE)
+    _, out1, cell1 = _fwd(lib, train, pre, Wh, h0, c0)
+    ifgo2, out2, cell2 = _fwd(lib, infer, pre, Wh, h0, c0)
+    assert torch.equal(out1, out2)
+    assert torch.equal(cell1[T], cell2[T])
+    assert torch.equal(ifgo2, pre), "inference mode wrote the saved pre-activations"
+    if T > 1:
+        assert float(cell2[1:T].abs().max()) == 0.0, "inference mode wrote cell[1..T-1]"
