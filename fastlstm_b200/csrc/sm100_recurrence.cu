@@ -93,12 +93,13 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   if (p.nb_par > p.nbt) p.nb_par = p.nbt;
   p.ntl = cdiv(p.nbt, p.nb_par);
   p.TI = p.ntl >= 3 ? 4 : p.ntl >= 2 ? 2 : 1;     // batch tiles interleaved per CTA (state: cell rows in registers)
-  if (UH == 32 && p.TI > 2) p.TI = 2;             // 16 units per thread: four tiles' cell rows would spill
   p.grid = p.nh * p.nb_par;
   p.epi_warps = (UH == 16 && p.TI == 1) ? 4 : 8;
   // a single 16-unit tile in flight is latency bound: four issuers next to one epilogue warpgroup
   // (9 warps); otherwise two issuers, eight epilogue warps and, for interleaved tiles, the publisher
-  const int n_issuers = (UH == 16 && p.TI == 1) ? 4 : 2;
+  // (interleaved 32-unit slices: N = 128 runs the tensor pipe at full rate from ONE issuing thread, and a
+  // single accumulator per item leaves tensor-memory columns for the cell rows of four tiles)
+  const int n_issuers = (UH == 16 && p.TI == 1) ? 4 : (UH == 32 && p.TI >= 2) ? 1 : 2;
   const int n_publisher = p.TI >= 2 ? 1 : 0;
   p.threads = 32 * (1 + n_issuers + n_publisher + p.epi_warps);   // producer + MMA issuers [+ publisher] + epilogue
   // Wh slice resident in shared memory when it fits next to a useful ring; otherwise (H > 1024)
@@ -210,7 +211,7 @@ struct ItemCursor {
 // warps - at most 12 (3 per SM sub-partition), which leaves 168 registers per thread; a 13th would cap
 // them at 128.  The epilogue must not spill.
 template <int UH, int TI, typename T16>
-__global__ void __launch_bounds__(32 * (UH == 16 && TI == 1 ? 9 : (TI >= 2 ? 12 : 11)), 1)
+__global__ void __launch_bounds__(32 * (UH == 16 && TI == 1 ? 9 : (TI >= 2 ? (UH == 32 ? 11 : 12) : 11)), 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmH,
            const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmC, const FwdParams p) {
   constexpr int N = 4 * UH;
@@ -258,9 +259,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   // stalls its thread for a memory round trip, so a PUBLISHER warp does the releasing (and the proxy
   // fence of the hand-off): the epilogue warps only arrive on a CTA-local barrier after storing h.
   constexpr bool PUBLISHER = (TI >= 2);
-  constexpr int NACC = (UH == 16 && TI == 1) ? 4 : 2;   // issuer warps / partial accumulators
+  constexpr int NACC = (UH == 16 && TI == 1) ? 4 : (UH == 32 && TI >= 2) ? 1 : 2;   // issuer warps / partial accumulators
   constexpr int FIRST_EPI = 1 + NACC + (PUBLISHER ? 1 : 0);   // first epilogue warp
-  constexpr int ACC_STRIDE = 256;                   // columns per item buffer (NACC * N <= 256)
+  // Columns per item buffer (NACC * N <= 256).  Interleaved tiles pack the two buffers into the first
+  // 256 columns and keep the tiles' cell rows (fp32, a column per unit) in the columns behind them.
+  constexpr int ACC_STRIDE = (TI >= 2) ? NACC * N : 256;
+  constexpr int C_BASE = 2 * ACC_STRIDE;
+  static_assert(TI == 1 || C_BASE + TI * UH <= 512, "cell rows do not fit the tensor memory");
   constexpr uint32_t TMEM_COLS = 512;
   const int nacc = p.ni;                             // accumulators / issuers / TMA lanes in use
 
@@ -453,19 +458,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       for (int i = 0; i < npb; ++i) issue_load();
     int it = 0;                             // items consumed
     bool ok = true;
+    // cell rows of this thread's (row, NU units) for tile slot j: tensor-memory columns behind the accumulators
+    const uint32_t c_taddr = tmem_base + C_BASE + (uint32_t(q * 32) << 16) + ug * NU;
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
-      float c[TI][NU];
 #pragma unroll
       for (int j = 0; j < TI; ++j) {
         const int bt = pb + (ch * TI + j) * p.nb_par;
         const int row = bt * RB + row_in_tile;
 #pragma unroll
-        for (int u = 0; u < NU; ++u) c[j][u] = 0.f;
-        if (bt < p.nbt && row < p.B) {
+        for (int v = 0; v < NPIECE; ++v) {
+          float c0[8];
 #pragma unroll
-          for (int v = 0; v < NPIECE; ++v) unpack8<T16>(ldg16(cell + (size_t)row * H + unit0 + 8 * v), &c[j][8 * v]);
+          for (int u = 0; u < 8; ++u) c0[u] = 0.f;
+          if (bt < p.nbt && row < p.B) unpack8<T16>(ldg16(cell + (size_t)row * H + unit0 + 8 * v), c0);
+          uint32_t cr[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) cr[u] = __float_as_uint(c0[u]);
+          tmem_st_32x8(c_taddr + j * UH + 8 * v, cr);
         }
       }
+      tmem_st_wait();
       for (int t = 0; t < p.T && ok; ++t) {
 #pragma unroll
         for (int j = 0; j < TI; ++j) {
@@ -488,6 +500,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 #pragma unroll
           for (int v = 0; v < NPIECE; ++v) {
             float pa[4][8];
+            uint32_t cr[8];
+            tmem_ld_32x8(c_taddr + j * UH + 8 * v, cr);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint32_t acc[NACC][8];
@@ -520,13 +534,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                 pa[g][2 * u + 1] += f2.y;
               }
             }
-            float hv[8];
+            float hv[8], cv[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-              const float cn = sigmoid_fast(pa[1][u]) * c[j][8 * v + u] + sigmoid_fast(pa[0][u]) * tanh_fast(pa[2][u]);
-              c[j][8 * v + u] = cn;
+              const float cn = sigmoid_fast(pa[1][u]) * __uint_as_float(cr[u]) + sigmoid_fast(pa[0][u]) * tanh_fast(pa[2][u]);
+              cv[u] = cn;
+              cr[u] = __float_as_uint(cn);
               hv[u] = sigmoid_fast(pa[3][u]) * tanh_fast(cn);
             }
+            tmem_st_32x8(c_taddr + j * UH + 8 * v, cr);
             if (row_ok) store8<T16>(out + o1 + 8 * v, hv);
             // final pre-activations back in place, cell row into its buffer (16-bit, as stored)
 #pragma unroll
@@ -535,9 +551,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                   make_uint4(pk2<T16>(pa[g][0], pa[g][1]), pk2<T16>(pa[g][2], pa[g][3]), pk2<T16>(pa[g][4], pa[g][5]),
                              pk2<T16>(pa[g][6], pa[g][7]));
             *reinterpret_cast<uint4*>(cbuf + c_off(v)) =
-                make_uint4(pk2<T16>(c[j][8 * v], c[j][8 * v + 1]), pk2<T16>(c[j][8 * v + 2], c[j][8 * v + 3]),
-                           pk2<T16>(c[j][8 * v + 4], c[j][8 * v + 5]), pk2<T16>(c[j][8 * v + 6], c[j][8 * v + 7]));
+                make_uint4(pk2<T16>(cv[0], cv[1]), pk2<T16>(cv[2], cv[3]), pk2<T16>(cv[4], cv[5]), pk2<T16>(cv[6], cv[7]));
           }
+          tmem_st_wait();
           // publish h[t+1] first (it is all the peers wait for): the publisher warp fences and releases
           __syncwarp();
           if (lane == 0) mbar_arrive(&pub_bar[(it - 1) & 3]);
@@ -761,7 +777,7 @@ static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensor
 // does (thread = batch row x 8 units: dc carried in fp32 registers, d_ifgo[t-1] written and
 // published with the same per-(step, batch tile) arrival counters as the forward kernel).
 // =====================================================================================
-constexpr int DB_PARTS = 256;             // row groups of the bias-gradient column sum
+constexpr int DB_PARTS = 1024;            // row groups of the bias-gradient column sum
 constexpr int XROW_BYTES = 64;            // one row of a slice: 16 fp32; its four 16-byte pieces are XOR-swizzled
 constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x 16 fp32 = 8 KB
 
@@ -1639,6 +1655,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   BLSTM_FWD_CASE(16, 4)
   BLSTM_FWD_CASE(32, 1)
   BLSTM_FWD_CASE(32, 2)
+  BLSTM_FWD_CASE(32, 4)
 #undef BLSTM_FWD_CASE
   return BLSTM_E_UNSUPPORTED;
 }
