@@ -107,9 +107,9 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.w_bytes = (size_t)p.N * H * 2;
   p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;
   p.stage_bytes = R_STAGE_BYTES + (p.ws ? (size_t)p.N * 128 : 0);
-  // Interleaved tiles: the epilogue's global traffic goes through TMA.  Every epilogue warp owns
+  // Interleaved tiles: the epilogue's gate traffic goes through TMA.  Every epilogue warp owns
   // landing buffers for its 32 rows' projected pre-activations (4 gates x NU units; the final
-  // pre-activations are written back in place and stored from there) and one for the cell rows.
+  // pre-activations are written back in place and stored from there).
   // Two landing buffers per warp (the next item's box is fetched a whole item ahead) when the ring
   // still gets four stages, else one.
   p.npb = 0;
@@ -117,9 +117,9 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   size_t fixed = 1024 + (p.ws ? 0 : p.w_bytes) + 512;
   if (p.TI >= 2) {
     const int NU = 4 * UH / p.epi_warps;
-    const size_t pb = 256 * (size_t)NU, cb = 64 * (size_t)NU;
-    p.npb = (fixed + p.epi_warps * (2 * pb + cb) + 4 * p.stage_bytes <= 232448) ? 2 : 1;
-    p.ep_bytes = p.epi_warps * (p.npb * pb + cb);
+    const size_t pb = 256 * (size_t)NU;
+    p.npb = (fixed + p.epi_warps * 2 * pb + 4 * p.stage_bytes <= 232448) ? 2 : 1;
+    p.ep_bytes = p.epi_warps * p.npb * pb;
     fixed += p.ep_bytes;
   }
   if (!pick_ring(fixed, p.stage_bytes, n_issuers, H / RK, &p.stages, &p.ni)) return p;
@@ -213,14 +213,14 @@ struct ItemCursor {
 template <int UH, int TI, typename T16>
 __global__ void __launch_bounds__(32 * (UH == 16 && TI == 1 ? 9 : (TI >= 2 ? (UH == 32 ? 11 : 12) : 11)), 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmH,
-           const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmC, const FwdParams p) {
+           const __grid_constant__ CUtensorMap tmP, const FwdParams p) {
   constexpr int N = 4 * UH;
   // Interleaved tiles are throughput bound, and there the epilogue's row-strided 16-byte global
   // accesses (a thread owns a batch row: 32 sectors per warp instruction) were the bottleneck: the
-  // projected pre-activations come in, and the final pre-activations and cell rows go out, as TMA
-  // boxes through shared memory, one set of buffers per epilogue warp (tmP: ifgo as
-  // {unit, row, gate, step}, tmC: cell as {unit, row, step}).  Only h keeps its direct stores: they
-  // are what the step hand-off orders.
+  // projected pre-activations come in, and the final pre-activations go out, as TMA boxes through
+  // shared memory, one set of buffers per epilogue warp (tmP: ifgo as {unit, row, gate, step}): eight
+  // of the twelve 16-byte accesses a thread makes per 8 units.  h keeps its direct stores (they are
+  // what the step hand-off orders) and so do the cell rows (a buffer for them would cost a ring stage).
   constexpr bool TMAEP = (TI >= 2);
   // Epilogue warps.  A single tile of 16 units is latency bound and runs best as one warpgroup with
   // 16 units per thread next to four issuers (9 warps); every other shape uses two warpgroups that
@@ -283,7 +283,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmH);
-    if (TMAEP) { tma_prefetch_desc(&tmP); tma_prefetch_desc(&tmC); }
+    if (TMAEP) tma_prefetch_desc(&tmP);
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -308,14 +308,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     int gs = 0;                // ring position of the current item's chunk 0
     uint32_t gph = 0;
     bool ok = true;
+    // With interleaved tiles an item's arrival counter is usually complete long before its turn, and
+    // what costs is the round trip of looking: lane 31 reads the NEXT item's counter while the other
+    // lanes issue the current item's loads, and lane 0 only spins when that early look found it incomplete.
+    ItemCursor<TI> nx;
+    nx.init();
+    bool nx_valid = nx.next(pb, p.nb_par, p.nbt, n_chunks, p.T);   // the first item itself
+    int early = 0;             // lane 31: early reading of the next item's counter
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
       for (int t = 0; t < p.T && ok; ++t) {
         for (int j = 0; j < TI && ok; ++j) {
           const int bt = pb + (ch * TI + j) * p.nb_par;
           if (bt >= p.nbt) continue;
+          // what lane 31 read for this item while the previous item's loads were being issued
+          const int early_now = (TI >= 2) ? __shfl_sync(0xffffffffu, early, 31) : 0;
+          if (TI >= 2) nx_valid = nx_valid && nx.next(pb, p.nb_par, p.nbt, n_chunks, p.T);
           if (t > 0) {   // h[t] of this batch tile complete: every epilogue warp of every hidden tile arrived
             int seen = 1;
-            if (lane == 0) {
+            if (lane == 0 && !(TI >= 2 && early_now >= p.flag_target)) {
               wc.d0 = t; wc.d1 = bt;
               seen = wait_flag_ge(&p.flags[(size_t)t * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, t, bt) ? 1 : 0;
             }
@@ -339,6 +349,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               tma_load_3d(a_s + (size_t)s * SB, &tmH, &full[s], kc * RK, row0, t);
               if (p.ws) tma_load_3d(a_s + (size_t)s * SB + R_STAGE_BYTES, &tmW, &full[s], kc * RK, ht * UH, 0);
             }
+          } else if (TI >= 2 && lane == 31) {
+            // (the other arm of the same branch: the issuing lanes do not wait for this read)
+            early = 0;
+            if (nx_valid && nx.t > 0) early = ld_acquire_gpu(&p.flags[(size_t)nx.t * p.nbt + nx.tile(pb, p.nb_par)]);
           }
           if (__any_sync(0xffffffffu, !lane_ok)) { ok = false; break; }
           gs += KC;
@@ -423,11 +437,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   } else if constexpr (TMAEP) {
     // ---------------------------------------------------------------- epilogue, interleaved tiles
     // thread = (batch row, NU units), worked in passes of 8 units.  Each warp owns `npb` landing
-    // buffers [4 gates][32 rows][NU units] and one cell buffer [32 rows][NU units]: rows of 16 bytes
-    // lie back to back, rows of 32 bytes carry the 32-byte swizzle, so the 32 lanes' 16-byte pieces of
-    // one gate fall into different banks.  Lane 0 issues the warp's TMA loads (`npb` items ahead) and
-    // stores.
-    constexpr int PB_BYTES = 256 * NU, CB_BYTES = 64 * NU, NPIECE = NU / 8;
+    // buffers [4 gates][32 rows][NU units]: rows of 16 bytes lie back to back, rows of 32 bytes carry
+    // the 32-byte swizzle, so the 32 lanes' 16-byte pieces of one gate fall into different banks.
+    // Lane 0 issues the warp's TMA loads (`npb` items ahead) and stores.
+    constexpr int PB_BYTES = 256 * NU, NPIECE = NU / 8;
     const int ew = warp - FIRST_EPI;
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int ug = ew >> 2;
@@ -435,10 +448,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     const int unit0 = ht * UH + ug * NU;
     const int npb = p.npb;
     uint8_t* pbuf = ep_s + (size_t)ew * npb * PB_BYTES;
-    uint8_t* cbuf = ep_s + (size_t)EW * npb * PB_BYTES + (size_t)ew * CB_BYTES;
     uint64_t* pfull = pre_full + 2 * ew;
     T16* out = reinterpret_cast<T16*>(p.out);
-    const T16* cell = reinterpret_cast<const T16*>(p.cell);
+    T16* cell = reinterpret_cast<T16*>(p.cell);
     auto c_off = [&](int v) { return (NU == 16) ? lane * 32 + ((v ^ ((lane >> 2) & 1)) * 16) : lane * 16; };
     auto p_off = [&](int g, int v) { return g * (64 * NU) + c_off(v); };
     // the load cursor runs `npb` items ahead of the item being worked on (lane 0 only)
@@ -544,27 +556,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             }
             tmem_st_32x8(c_taddr + j * UH + 8 * v, cr);
             if (row_ok) store8<T16>(out + o1 + 8 * v, hv);
-            // final pre-activations back in place, cell row into its buffer (16-bit, as stored)
+            // final pre-activations back in place (16-bit, as stored)
 #pragma unroll
             for (int g = 0; g < 4; ++g)
               *reinterpret_cast<uint4*>(pbb + p_off(g, v)) =
                   make_uint4(pk2<T16>(pa[g][0], pa[g][1]), pk2<T16>(pa[g][2], pa[g][3]), pk2<T16>(pa[g][4], pa[g][5]),
                              pk2<T16>(pa[g][6], pa[g][7]));
-            *reinterpret_cast<uint4*>(cbuf + c_off(v)) =
-                make_uint4(pk2<T16>(cv[0], cv[1]), pk2<T16>(cv[2], cv[3]), pk2<T16>(cv[4], cv[5]), pk2<T16>(cv[6], cv[7]));
+            if (row_ok && (!p.inference || t == p.T - 1)) store8<T16>(cell + o1 + 8 * v, cv);
           }
           tmem_st_wait();
           // publish h[t+1] first (it is all the peers wait for): the publisher warp fences and releases
           __syncwarp();
           if (lane == 0) mbar_arrive(&pub_bar[(it - 1) & 3]);
-          // then hand the two boxes to TMA and, once they have been read out of shared memory, fetch
-          // the box of the item `npb` ahead into the landing buffer that just became free
+          // then hand the box to TMA and, once it has been read out of shared memory, fetch the box of
+          // the item `npb` ahead into the landing buffer that just became free
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
             const int row0 = bt * RB + q * 32;
             if (!p.inference) tma_store_4d(&tmP, pbb, unit0, row0, 0, t);
-            if (!p.inference || t == p.T - 1) tma_store_3d(&tmC, cbuf, unit0, row0, t + 1);
             tma_store_commit();
             tma_store_wait_read<0>();
             issue_load();
@@ -754,10 +764,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
 
 template <int UH, int TI, typename T16>
 static int launch_fwd_t(const RecPlan& pl, const CUtensorMap& tw, const CUtensorMap& th, const CUtensorMap& tp,
-                        const CUtensorMap& tc, FwdParams& p, cudaStream_t st) {
+                        FwdParams& p, cudaStream_t st) {
   auto kern = fwd_kernel<UH, TI, T16>;
   BLSTM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-  void* args[] = {(void*)&tw, (void*)&th, (void*)&tp, (void*)&tc, (void*)&p};
+  void* args[] = {(void*)&tw, (void*)&th, (void*)&tp, (void*)&p};
   BLSTM_CUDA_OK(cudaLaunchCooperativeKernel((void*)kern, dim3(pl.grid), dim3(pl.threads), args, pl.smem, st));
   count_launch();
   return BLSTM_OK;
@@ -815,15 +825,15 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   // Cluster exchange: receive slots (3 peers x 8 KB) and send staging (3 x 8 KB), one set.  With
   // interleaved tiles a CTA tells its three peers when it has consumed an item's slices, and nobody
   // stages or ships the next item before all three have said so (`consumed` in the kernel).
-  // Interleaved tiles also move the epilogue's gate traffic through TMA: two landing buffers per
+  // Interleaved tiles also move the epilogue's gate traffic through TMA: three landing buffers per
   // epilogue warp (32 rows x 4 gates x 8 units; d_ifgo is written back in place and stored from there).
   p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
-  p.ep_bytes = p.TI >= 2 ? (size_t)8 * 2 * 2048 : 0;
-  if (1024 + wres + p.recv_bytes + p.ep_bytes + 512 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
+  p.ep_bytes = p.TI >= 2 ? (size_t)8 * 3 * 2048 : 0;
+  if (1024 + wres + p.recv_bytes + p.ep_bytes + 1024 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
     p.TI = 1;                                               // not enough room to interleave tiles
     p.ep_bytes = 0;
   }
-  size_t fixed = 1024 + wres + p.recv_bytes + p.ep_bytes + 512;   // 512: barriers and counters behind the ring
+  size_t fixed = 1024 + wres + p.recv_bytes + p.ep_bytes + 1024;  // 1024: barriers and counters behind the ring
   // warps: 1 producer + 3 MMA issuers (or 2 + a publisher warp when tiles are interleaved) + 2 epilogue
   // warpgroups = 12 (3 per SM sub-partition, 168 registers each); a 13th warp would cap every thread
   // at 128 registers.
@@ -837,7 +847,7 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.alias = 0;
   if (p.TI == 1 && p.stages < 6) {
     int st2 = 0, ni2 = 0;
-    const size_t fixed2 = 1024 + wres + 512;
+    const size_t fixed2 = 1024 + wres + 1024;
     if (pick_ring(fixed2, p.stage_bytes, n_issuers, H / RK, &st2, &ni2) && st2 > p.stages &&
         (size_t)st2 * p.stage_bytes >= p.recv_bytes) {
       p.alias = 1; p.stages = st2; p.ni = ni2; fixed = fixed2;
@@ -923,7 +933,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint8_t* recv = smem + (p.ws ? 0 : (size_t)H * 128);                     // [3 senders][128 rows][64 B]
   constexpr int XB = 1;                                       // one set of exchange buffers
   uint8_t* stage = recv + (size_t)XB * 3 * XSLOT_BYTES;      // [3 receivers][128 rows][64 B]
-  uint8_t* ep_s = stage + (size_t)XB * 3 * XSLOT_BYTES;      // epilogue TMA buffers [8 warps][2][2 KB]
+  uint8_t* ep_s = stage + (size_t)XB * 3 * XSLOT_BYTES;      // epilogue TMA buffers [8 warps][3][2 KB]
   uint8_t* a_s = p.alias ? recv : ep_s + p.ep_bytes;         // ring (over the exchange buffers if aliased)
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;
@@ -939,7 +949,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint64_t* pub_bar = reinterpret_cast<uint64_t*>(pub_cnt + 4);   // [4] item published? by item index mod 4
   uint64_t* rdy = pub_bar + 4;                                 // aliased buffers: the 3 peers are done with their MMAs
   uint64_t* consumed = rdy + 1;                                // interleaved tiles: the 3 peers' 8 warps read an item's slices
-  uint64_t* pre_full = consumed + 1;                           // [8 epilogue warps][2] landing buffer filled
+  uint64_t* pre_full = consumed + 1;                           // [8 epilogue warps][3] landing buffer filled
+  uint64_t* pre_free = pre_full + 24;                          // [8 epilogue warps][3] landing buffer may be refilled
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t r = cluster_ctarank();                       // gate whose K range this CTA owns
@@ -960,7 +971,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], ITEM_WARPS);
     mbar_init(rdy, 3);
     mbar_init(consumed, 3 * ITEM_WARPS);
-    for (int i = 0; i < 16; ++i) mbar_init(&pre_full[i], 1);
+    for (int i = 0; i < 24; ++i) { mbar_init(&pre_full[i], 1); mbar_init(&pre_free[i], 1); }
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
     tma_prefetch_desc(&tmW);
@@ -989,14 +1000,23 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     int gs = 0;
     uint32_t gph = 0;
     bool ok = true;
+    // With interleaved tiles an item's arrival counter is usually complete long before its turn, and
+    // what costs is the round trip of looking: lane 31 reads the NEXT item's counter while the other
+    // lanes issue the current item's loads, and lane 0 only spins when that early look found it incomplete.
+    ItemCursor<TI> nx;
+    nx.init();
+    bool nx_valid = nx.next(pb, p.nb_par, p.nbt, n_chunks, T);   // the first item itself
+    int early = 0;             // lane 31: early reading of the next item's counter
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
       for (int st = 1; st <= T && ok; ++st) {
         const int tg = T - st;      // timestep whose d_ifgo is streamed
         for (int j = 0; j < TI && ok; ++j) {
           const int bt = pb + (ch * TI + j) * p.nb_par;
           if (bt >= p.nbt) continue;
+          const int early_now = (TI >= 2) ? __shfl_sync(0xffffffffu, early, 31) : 0;
+          if (TI >= 2) nx_valid = nx_valid && nx.next(pb, p.nb_par, p.nbt, n_chunks, T);
           int seen = 1;
-          if (lane == 0) {
+          if (lane == 0 && !(TI >= 2 && early_now >= p.flag_target)) {
             wc.d0 = tg; wc.d1 = bt;
             seen = wait_flag_ge(&p.flags[(size_t)tg * p.nbt + bt], p.flag_target, p.ctl, p.limit_ns, tg, bt) ? 1 : 0;
           }
@@ -1019,6 +1039,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               tma_load_3d(a_s + (size_t)s * SB, &tmG, &full[s], col0 + kc * RK, row0, tg);
               if (p.ws) tma_load_2d(a_s + (size_t)s * SB + R_STAGE_BYTES, &tmW, &full[s], ugc * 64, col0 + kc * RK);
             }
+          } else if (TI >= 2 && lane == 31) {
+            // (the other arm of the same branch: the issuing lanes do not wait for this read)
+            early = 0;
+            if (nx_valid) early = ld_acquire_gpu(&p.flags[(size_t)(T - 1 - nx.t) * p.nbt + nx.tile(pb, p.nb_par)]);
           }
           if (__any_sync(0xffffffffu, !lane_ok)) { ok = false; break; }
           gs += KC;
@@ -1050,6 +1074,30 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             ++k;
           }
         }
+      }
+    } else if (TMAEP && lane <= ITEM_WARPS) {
+      // ------------------------------------------------------------ gate loaders (lanes 1..8)
+      // Lane 1+w fetches epilogue warp w's gate boxes, up to three gate-maths items ahead, into the
+      // warp's three landing buffers in turn; a buffer is refilled once the warp has said that the
+      // d_ifgo box it held has been written (pre_free).  Issuing these loads from here rather than
+      // from the epilogue warps matters: a TMA issue waits for room behind the producer's 16 KB
+      // boxes (about a thousand clocks), which the epilogue warps cannot afford.
+      const int w = lane - 1;
+      const int gq = (FIRST_EPI + w) & 3, gu = w >> 2;          // the warp's row quarter and unit half
+      const int g_unit0 = ugc * 64 + (int)r * 16 + gu * 8;
+      uint8_t* g_buf = ep_s + (size_t)w * 3 * 2048;
+      ItemCursor<TI> lc;
+      lc.init();
+      int n = 0;
+      bool ok = true;
+      while (ok && lc.next(pb, p.nb_par, p.nbt, n_chunks, T)) {
+        const int b = n % 3;
+        wc.d0 = T - 1 - lc.t; wc.d1 = lc.tile(pb, p.nb_par);
+        if (n >= 3 && !mbar_wait(&pre_free[3 * w + b], (uint32_t)(n / 3 - 1) & 1u, wc)) { ok = false; break; }
+        mbar_expect_tx(&pre_full[3 * w + b], 2048);
+        tma_load_4d(g_buf + b * 2048, &tmI, &pre_full[3 * w + b], g_unit0, lc.tile(pb, p.nb_par) * RB + gq * 32, 0,
+                    T - 1 - lc.t);
+        ++n;
       }
     }
   } else if (warp < 1 + NACC) {
@@ -1120,26 +1168,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     int it = 0;                 // MMA items consumed so far: TMEM buffer it & 1, on its (it >> 1)-th use
     int pub_it = 0;             // gate-maths items published so far
     bool ok = true;
-    // Interleaved tiles: this warp's two landing buffers [4 gates][32 rows][8 units] (16-byte rows back
-    // to back: the 32 lanes' pieces of one gate fall into different banks); lane 0 issues the warp's
-    // TMA loads two gate-maths items ahead, and its stores.
+    // Interleaved tiles: this warp's three landing buffers [4 gates][32 rows][8 units] (16-byte rows
+    // back to back: the 32 lanes' pieces of one gate fall into different banks), used in turn by
+    // consecutive gate-maths items; a lane of the publisher warp issues the warp's TMA loads, lane 0 of
+    // the warp its stores.  An item's store is only waited for one item later (by then it has long
+    // completed): that is when its buffer is handed back to the loader and when the warp counts the
+    // item in.
     const int ew = warp - FIRST_EPI;
-    uint8_t* pbuf = ep_s + (size_t)ew * 2 * 2048;
-    uint64_t* pfull = pre_full + 2 * ew;
+    uint8_t* pbuf = ep_s + (size_t)ew * 3 * 2048;
+    uint64_t* pfull = pre_full + 3 * ew;
+    bool pending = false;             // lane 0: the previous item's store has not been waited for yet
     auto p_off = [&](int k) { return k * 512 + lane * 16; };
-    ItemCursor<TI> lc;
-    lc.init();
-    bool lc_valid = TMAEP && lc.next(pb, p.nb_par, p.nbt, n_chunks, T);
-    int n_loaded = 0;
-    auto issue_load = [&]() {
-      if (!lc_valid) return;
-      const int b = n_loaded & 1;
-      mbar_expect_tx(&pfull[b], 2048);
-      tma_load_4d(pbuf + b * 2048, &tmI, &pfull[b], unit0, lc.tile(pb, p.nb_par) * RB + q * 32, 0, T - 1 - lc.t);
-      ++n_loaded;
-      lc_valid = lc.next(pb, p.nb_par, p.nbt, n_chunks, T);
-    };
-    if (TMAEP && lane == 0) { issue_load(); issue_load(); }
+    uint64_t* pfree = pre_free + 3 * ew;
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
       // dc is carried per interleaved tile; dh is rebuilt from the accumulator in every item, so one
       // copy serves all tiles (its first value, the gradient of h_n, is fetched in the tile's first item)
@@ -1223,8 +1263,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       // interleaved tiles: the gates of the item whose maths comes next, out of its landing buffer
       auto fetch_gates = [&]() -> bool {
         if constexpr (TMAEP) {
-          if (!mbar_wait(&pfull[pub_it & 1], (uint32_t)(pub_it >> 1) & 1u, wc)) return false;
-          const uint8_t* pbb = pbuf + (pub_it & 1) * 2048;
+          if (!mbar_wait(&pfull[pub_it % 3], (uint32_t)(pub_it / 3) & 1u, wc)) return false;
+          const uint8_t* pbb = pbuf + (pub_it % 3) * 2048;
 #pragma unroll
           for (int k = 0; k < 4; ++k) pf[k] = *reinterpret_cast<const uint4*>(pbb + p_off(k));
         }
@@ -1252,7 +1292,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if constexpr (TI >= 2) {
               // the previous item's slices have been read by all three peers (so the staging below
               // overwrites nothing a copy still reads, and the peers' receive slots are free again)
-              if (it > 1 && !mbar_wait_cluster(consumed, (uint32_t)it & 1u, wc)) { ok = false; break; }
+              // (no data rides on this barrier, so a plain CTA-scope wait will do)
+              if (it > 1 && !mbar_wait(consumed, (uint32_t)it & 1u, wc)) { ok = false; break; }
             }
             if (p.alias && shipper) {
               // this item's MMAs are done (their reads of the ring completed before acc_full did), so
@@ -1410,10 +1451,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               }
             }
             if constexpr (TMAEP) {
-              // d_ifgo[t] goes back into the landing buffer the gates came from and leaves as one box;
-              // once it has been read out the buffer takes the gates of the item two ahead, and once it
-              // has been written (the peers' producers read it next) the warp counts the item in
-              uint8_t* pbb = pbuf + (pub_it & 1) * 2048;
+              // d_ifgo[t] goes back into the landing buffer the gates came from and leaves as one box.
+              // The PREVIOUS item's box has been written by now: its buffer takes the gates of the item
+              // two ahead, and (the peers' producers read d_ifgo next) the warp counts that item in.
+              uint8_t* pbb = pbuf + (pub_it % 3) * 2048;
               *reinterpret_cast<uint4*>(pbb + p_off(0)) = make_uint4(qi[0], qi[1], qi[2], qi[3]);
               *reinterpret_cast<uint4*>(pbb + p_off(1)) = make_uint4(qf[0], qf[1], qf[2], qf[3]);
               *reinterpret_cast<uint4*>(pbb + p_off(2)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
@@ -1423,9 +1464,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               if (lane == 0) {
                 tma_store_4d(&tmD, pbb, unit0, bt * RB + q * 32, 0, t);
                 tma_store_commit();
-                tma_store_wait_read<0>();
-                issue_load();
-                tma_store_wait<0>();
+                // The wait may only be put off while the next item does not need THIS one: not when this
+                // CTA walks a single tile in this chunk (the tile's next step is the next item), nor in
+                // the chunk's last step (the closing items store nothing, so nobody would publish it).
+                const bool now = (pb + (ch * TI + 1) * p.nb_par >= p.nbt) || st == T - 1;
+                if (now) tma_store_wait<0>(); else tma_store_wait<1>();   // <1>: all but the store just issued
+                if (pending) { mbar_arrive(&pfree[(pub_it - 1) % 3]); mbar_arrive(&pub_bar[(pub_it - 1) & 3]); }
+                if (now) { mbar_arrive(&pfree[pub_it % 3]); mbar_arrive(&pub_bar[pub_it & 3]); }
+                pending = !now;
               }
             } else if (row_ok) {
               T16* dstp = dg + ((size_t)t * p.B + row) * H4 + unit0;
@@ -1442,7 +1488,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             // (a warp can be at most four items ahead of another - the maths-only items that open a
             // chunk - so four counters never mix items)
             if (lane == 0) {
-              if constexpr (PUBLISHER) {
+              if constexpr (TMAEP) {
+                // counted in above, once the store has completed
+              } else if constexpr (PUBLISHER) {
                 mbar_arrive(&pub_bar[pub_it & 3]);      // the publisher warp releases for the CTA
               } else {
                 const bool pub = !p.cta_publish ||
@@ -1469,6 +1517,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           }
         }
       }
+    }
+    if (TMAEP && lane == 0) {
+      tma_store_wait<0>();
+      if (pending) { mbar_arrive(&pfree[(pub_it - 1) % 3]); mbar_arrive(&pub_bar[(pub_it - 1) & 3]); }
     }
   }
   // ---------------------------------------------------------------- teardown
@@ -1605,7 +1657,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
     rc = encode_tensor_map(&th, out, 3, dims, str, box);
     if (rc) return rc;
   }
-  CUtensorMap tp = th, tc = th;     // only read by the kernels that interleave tiles
+  CUtensorMap tp = th;              // only read by the kernels that interleave tiles
   if (pl.TI >= 2) {
     const int NU = 4 * pl.UH / pl.epi_warps;
     {  // ifgo [T,B,4H] as {unit, batch row, gate, t}: a box is one warp's 4 gates x 32 rows x NU units;
@@ -1614,13 +1666,6 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
       uint64_t str[3] = {(uint64_t)4 * H * 2, (uint64_t)H * 2, (uint64_t)B * 4 * H * 2};
       uint32_t box[4] = {(uint32_t)NU, 32, 4, 1};
       rc = encode_tensor_map(&tp, ifgo, 4, dims, str, box, 2, NU == 16 ? 32 : 0);
-      if (rc) return rc;
-    }
-    {  // cell [T+1,B,H] as {unit, batch row, t}
-      uint64_t dims[3] = {(uint64_t)H, (uint64_t)B, (uint64_t)(T + 1)};
-      uint64_t str[2] = {(uint64_t)H * 2, (uint64_t)B * H * 2};
-      uint32_t box[3] = {(uint32_t)NU, 32, 1};
-      rc = encode_tensor_map(&tc, cell, 3, dims, str, box, 2, NU == 16 ? 32 : 0);
       if (rc) return rc;
     }
   }
@@ -1648,8 +1693,8 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   const bool bf = d.dtype == BLSTM_BF16;
 #define BLSTM_FWD_CASE(U, I)                                                                         \
   if (pl.UH == U && pl.TI == I)                                                                      \
-    return bf ? launch_fwd_t<U, I, __nv_bfloat16>(pl, tw, th, tp, tc, p, st)                         \
-              : launch_fwd_t<U, I, __half>(pl, tw, th, tp, tc, p, st);
+    return bf ? launch_fwd_t<U, I, __nv_bfloat16>(pl, tw, th, tp, p, st)                             \
+              : launch_fwd_t<U, I, __half>(pl, tw, th, tp, p, st);
   BLSTM_FWD_CASE(16, 1)
   BLSTM_FWD_CASE(16, 2)
   BLSTM_FWD_CASE(16, 4)
