@@ -17,6 +17,7 @@ DTYPE_CODE = {"fp32": F32, "fp16": F16, "bf16": BF16}
 PHASE_FWD, PHASE_BWD = 0, 1
 FLAG_FORCE_GENERIC = 1
 FLAG_INFERENCE = 8
+FLAG_NO_CLUSTER = 16      # forward: keep small hidden sizes on the general kernel
 FLAG_TEST_NO_ARRIVE = 4   # test hook: no CTA signals step completion (every wait runs out)
 
 OK = 0

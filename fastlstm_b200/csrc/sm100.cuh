@@ -25,6 +25,13 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
                          const void* ifgo, const void* cell, const void* Wh, void* d_ifgo, void* dh0,
                          void* dc0, float* db, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// Small hidden sizes (H = 64, 128, 256) with few batch tiles: the forward recurrence whose CTAs hand
+// h over inside one cluster per batch tile.  *taken = false when the shape (or the device's cluster
+// capacity) does not allow it and the general kernel has to run.  `ws` = zeroed control block.
+bool sm100_fwd_cluster_shape(const blstm_desc& d);
+int sm100_fwd_cluster(const blstm_desc& d, void* ifgo, const void* Wh, void* out, void* cell, void* ws,
+                      cudaStream_t st, bool* taken);
+
 // one-line description of the launch plan of a phase ("" when the tcgen05 kernels do not cover it)
 int sm100_plan_detail(const blstm_desc& d, int phase, char* buf, size_t n);
 

@@ -26,6 +26,7 @@
 #include "generic.cuh"
 #include "sm100.cuh"
 #include "sm100_common.cuh"
+#include "sm100_rec_util.cuh"
 
 namespace blstm {
 namespace sm100 {
@@ -152,42 +153,6 @@ struct FwdParams {
   void* out;                // [T+1,B,H]
   void* cell;               // [T+1,B,H]
 };
-
-template <typename T16> __device__ __forceinline__ float2 cvt2(uint32_t v);
-template <> __device__ __forceinline__ float2 cvt2<__half>(uint32_t v) {
-  return __half22float2(*reinterpret_cast<__half2*>(&v));
-}
-template <> __device__ __forceinline__ float2 cvt2<__nv_bfloat16>(uint32_t v) {
-  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
-}
-template <typename T16> __device__ __forceinline__ uint32_t pk2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pk2<__half>(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-template <> __device__ __forceinline__ uint32_t pk2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-__device__ __forceinline__ uint4 ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-__device__ __forceinline__ void stg16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
-
-template <typename T16>
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int u = 0; u < 4; ++u) { const float2 t = cvt2<T16>(w[u]); f[2 * u] = t.x; f[2 * u + 1] = t.y; }
-}
-template <typename T16>
-__device__ __forceinline__ void store8(T16* dst, const float* f) {
-  stg16(dst, make_uint4(pk2<T16>(f[0], f[1]), pk2<T16>(f[2], f[3]), pk2<T16>(f[4], f[5]), pk2<T16>(f[6], f[7])));
-}
-template <int NCOL>
-__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[NCOL]) {
-  if constexpr (NCOL == 16) tmem_ld_32x16(taddr, r); else tmem_ld_32x8(taddr, r);
-}
 
 // Position in a CTA's sequence of work items, which every role walks in the same order:
 //   for chunk (TI tiles) : for step in [0, steps) : for j in [0, TI) : tile pb + (chunk*TI + j)*nb_par
@@ -1628,6 +1593,9 @@ int sm100_plan_detail(const blstm_desc& d, int phase, char* buf, size_t n) {
   }
   const RecPlan p = make_plan(d, phase);
   if (!p.ok) return 0;
+  if (sm100_fwd_cluster_shape(d))
+    return snprintf(buf, n, "sm100 fwd cluster=%d (one per batch tile, h handed over in shared memory) UH=16 TI=1 grid=%d "
+                    "threads=288 wh=resident", d.hidden_size / 16, d.hidden_size / 16 * p.nbt);
   return snprintf(buf, n, "sm100 fwd UH=%d TI=%d grid=%d threads=%d stages=%d issuers=%d wh=%s smem=%zu", p.UH, p.TI,
                   p.grid, p.threads, p.stages, p.ni, p.ws ? "streamed" : "resident", p.smem);
 }
@@ -1670,6 +1638,11 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
     }
   }
   BLSTM_CUDA_OK(cudaMemsetAsync(ws, 0, pl.ws_bytes, st));
+  {  // small hidden sizes with few batch tiles: hand-off inside one cluster per tile
+    bool taken = false;
+    rc = sm100_fwd_cluster(d, ifgo, Wh, out, cell, ws, st, &taken);
+    if (rc || taken) return rc;
+  }
   FwdParams p;
   p.npb = pl.npb;
   p.ep_bytes = (int)pl.ep_bytes;

@@ -56,6 +56,9 @@ enum {
                                    pre-activations nor cell[1..T-1] (nothing is saved for backward);
                                    out[1..T] and cell[T] are still produced.  Halves the bytes a
                                    step moves (5*B*H*e instead of 10*B*H*e). */
+  BLSTM_FLAG_NO_CLUSTER = 16,   /* forward: do not use the cluster hand-off kernel that small hidden
+                                   sizes (H = 64, 128, 256 with at most 7 batch tiles) otherwise get;
+                                   for comparisons and tests */
   BLSTM_FLAG_TEST_NO_ARRIVE = 4 /* test hook: CTAs never signal step completion, so every
                                    cross-CTA wait runs into wait_limit_us and the launch ends
                                    with BLSTM_E_WAIT_TIMEOUT in the control block (no fault) */

@@ -243,3 +243,37 @@ def test_inference_flag_leaves_outputs_bit_identical(case):
     assert torch.equal(ifgo2, pre), "inference mode wrote the saved pre-activations"
     if T > 1:
         assert float(cell2[1:T].abs().max()) == 0.0, "inference mode wrote cell[1..T-1]"
+
+
+# one cluster of 4, 8 and 16 CTAs; ragged tile; seven tiles (the most clusters of 16 that fit at once)
+CLUSTER_SHAPES = [(7, 64, 64), (9, 100, 128), (12, 64, 256), (5, 896, 256), (1, 40, 256)]
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("shape", CLUSTER_SHAPES)
+def test_cluster_hand_off_forward_matches_general_kernel(dtype, shape):
+    """Small hidden sizes hand h over inside one cluster per batch tile (shared memory, no counters).
+    Against the general tcgen05 kernel on the same inputs (BLSTM_FLAG_NO_CLUSTER) the results may only
+    differ by the order of the fp32 partial sums, and both must agree with fp32 maths."""
+    lib = _lib.load()
+    T, B, H = shape
+    dt = TD[dtype]
+    g = torch.Generator(device="cuda").manual_seed(7 * B + H)
+    pre = torch.randn(T, B, 4 * H, generator=g, device="cuda").to(dt)
+    Wh = ((torch.rand(4 * H, H, generator=g, device="cuda") * 2 - 1) / H ** 0.5).to(dt)
+    h0 = (torch.randn(B, H, generator=g, device="cuda") * 0.3).to(dt)
+    c0 = (torch.randn(B, H, generator=g, device="cuda") * 0.3).to(dt)
+    import ctypes
+    buf = ctypes.create_string_buffer(512)
+    assert lib.blstm_plan_detail(_desc(dtype, T, B, H), 0, buf, 512) == 0 and b"cluster=" in buf.value, buf.value
+    ifgo, out, cell = _fwd(lib, _desc(dtype, T, B, H), pre, Wh, h0, c0)
+    ifgo2, out2, cell2 = _fwd(lib, _desc(dtype, T, B, H, _lib.FLAG_NO_CLUSTER), pre, Wh, h0, c0)
+    rg, ro, rc = _torch_fwd(pre, Wh, h0, c0)
+    tol = 4e-3 if dtype == "fp16" else 3e-2
+    _cmp("out vs fp32 maths", out[1:], ro, tol)
+    _cmp("cell vs fp32 maths", cell[1:], rc, tol * 2)
+    _cmp("ifgo vs fp32 maths", ifgo, rg, tol * 4)
+    _cmp("out vs general kernel", out, out2, tol)
+    _cmp("ifgo vs general kernel", ifgo, ifgo2, tol * 4)
+    ifgo3, out3, _ = _fwd(lib, _desc(dtype, T, B, H), pre, Wh, h0, c0)
+    assert torch.equal(out, out3) and torch.equal(ifgo, ifgo3)
