@@ -11,8 +11,9 @@ at 1/2/4/8 GPUs, so the same workload runs at every N (strong scaling).
 
   value     whole-job layer-tokens/s (L*B*T per step / time), inputs resident in HBM
   e2e       same metric through FastLSTM with pinned-host inputs copied in and the
-            step's results (the output sequence and the final hidden state) copied
-            back to pinned host memory inside the timed region
+            step's result (the final hidden state; with --e2e-copy-out also the whole
+            output sequence) copied back to pinned host memory inside the timed region;
+            the line says what stays on the device
   roofline  both persistent recurrence kernels timed alone with CUDA events; the
             slower one is reported as the dominant kernel
   cudnn     torch.nn.LSTM (cuDNN) on the same GPU, same dtype, same inputs and step
@@ -189,6 +190,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "cudnn"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cudnn", action="store_true", help="skip the same-GPU torch.nn.LSTM (cuDNN) timing")
+    ap.add_argument("--e2e-copy-out", action="store_true",
+                    help="end-to-end arm: also copy the whole output sequence back to pinned host memory every step "
+                         "(default: only the final hidden state; the sequence and the gradients stay on the device)")
     ap.add_argument("--seq-len", type=int, default=0,
                     help="override T (profiling aid: shorter captures; the line then names the override)")
     args = ap.parse_args()
@@ -234,7 +238,7 @@ def main():
         state = tuple((torch.randn(L, B, H, generator=gen) * cfg["h0"]).to(dt).to(dev) for _ in range(2))
     x_dev = x_host.to(dev).requires_grad_(cfg["bwd"])
     hn_host = torch.empty((L, B, H), dtype=dt, pin_memory=True)
-    out_host = torch.empty(shape, dtype=dt, pin_memory=True)
+    out_host = torch.empty(shape, dtype=dt, pin_memory=True) if args.e2e_copy_out else None
     # data-parallel runs: every layer's backward writes its fp32 weight gradients straight into its
     # segment of the bucket and starts that segment's allreduce; allreduce() waits and fills p.grad
     bucket = GradBucket(model) if (cfg["bwd"] and world > 1) else None
@@ -264,19 +268,23 @@ def main():
             "clocks": sampler.result()}), flush=True)
         return
 
-    def step(x):
+    def step(x, after_forward=None):
         if cfg["bwd"]:
             for p in model.parameters():
                 p.grad = None
             if x.grad is not None:
                 x.grad = None
             out, (hn, cn) = model(x, state)
+            if after_forward is not None:
+                after_forward(out, hn)
             out.backward(dout)
             if bucket is not None:
                 bucket.allreduce()
         else:
             with torch.no_grad():
                 out, (hn, cn) = model(x, state)
+            if after_forward is not None:
+                after_forward(out, hn)
         return out, hn
 
     # End-to-end input pipeline: every step's input is uploaded from pinned host memory into one of
@@ -302,16 +310,22 @@ def main():
         upload(k ^ 1)                                    # next step's input
         torch.cuda.current_stream().wait_event(uploaded[k])
         x = x_bufs[k].detach().requires_grad_(cfg["bwd"])
-        out, hn = step(x)
+
+        def results_home(out, hn):
+            # The step's result goes back to pinned host memory as soon as the forward pass has produced
+            # it: the final hidden state, on the compute stream.  The output sequence [T,B,H] and the
+            # gradients stay on the device (their consumers - the next layer, the loss, the optimizer -
+            # live there); --e2e-copy-out also sends the sequence home on a second copy stream, beside
+            # the backward pass.
+            if out_host is not None:
+                down_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(down_stream):
+                    out_host.copy_(out.detach(), non_blocking=True)
+                    out.record_stream(down_stream)
+            hn_host.copy_(hn.detach(), non_blocking=True)
+
+        step(x, results_home)
         consumed[k].record()
-        # the step's results go back to pinned host memory: the output sequence on a second copy
-        # stream (it overlaps the next step; the final synchronize of the timed region waits for it),
-        # the final hidden state on the compute stream
-        down_stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(down_stream):
-            out_host.copy_(out.detach(), non_blocking=True)
-            out.record_stream(down_stream)
-        hn_host.copy_(hn, non_blocking=True)
         pipe["i"] += 1
 
     def barrier():
@@ -465,9 +479,11 @@ def main():
         "us_per_timestep": ms_step * 1e3 / (T * L),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": x_host.numel() * es * world,
-                "d2h_bytes_per_step": (hn_host.numel() + out_host.numel()) * es * world,
-                "input_pipeline": "double-buffered upload on a copy stream, one upload per step; the output "
-                                  "sequence and h_n are copied back to pinned memory every step (gradients stay on the device)"},
+                "d2h_bytes_per_step": (hn_host.numel() + (out_host.numel() if out_host is not None else 0)) * es * world,
+                "input_pipeline": "double-buffered upload on a copy stream, one upload per step; h_n"
+                                  + (" and the output sequence are" if out_host is not None else " is")
+                                  + " copied back to pinned memory every step"
+                                  + ("" if out_host is not None else "; the output sequence [T,B,H] and the gradients stay on the device")},
         "gpu_launches": launches,
         "clocks": sampler.result(),
         "roofline": roof,

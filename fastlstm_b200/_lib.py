@@ -14,9 +14,10 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfastlstm
 ABI_VERSION = 1
 F32, F16, BF16 = 0, 1, 2
 DTYPE_CODE = {"fp32": F32, "fp16": F16, "bf16": BF16}
-PHASE_FWD, PHASE_BWD = 0, 1
+PHASE_FWD, PHASE_BWD, PHASE_FWD_OP = 0, 1, 2
 FLAG_FORCE_GENERIC = 1
 FLAG_INFERENCE = 8
+FLAG_NO_FUSED = 32        # blstm_fwd: keep tiny sizes on projection + recurrence
 FLAG_NO_CLUSTER = 16      # forward: keep small hidden sizes on the general kernel
 FLAG_TEST_NO_ARRIVE = 4   # test hook: no CTA signals step completion (every wait runs out)
 

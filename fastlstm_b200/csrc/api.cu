@@ -137,6 +137,10 @@ size_t blstm_workspace_bytes(const blstm_desc* d, int phase) {
 
 const char* blstm_plan_name(const blstm_desc* d, int phase) {
   if (check_desc(d)) return "invalid";
+  if (phase == BLSTM_PHASE_FWD_OP) {
+    if (generic_fused_fwd_supported(*d)) return "fused";
+    phase = BLSTM_PHASE_FWD;
+  }
   return sm100_recurrence_supported(*d, phase) ? "sm100" : "generic";
 }
 
@@ -145,6 +149,14 @@ int blstm_plan_detail(const blstm_desc* d, int phase, char* buf, size_t buf_byte
   buf[0] = 0;
   int rc = check_desc(d);
   if (rc) return rc;
+  if (phase == BLSTM_PHASE_FWD_OP) {
+    if (generic_fused_fwd_supported(*d)) {
+      snprintf(buf, buf_bytes, "fused fwd (projection inside the time loop) rows_per_cta=4 grid=%d threads=%d",
+               (d->batch + 3) / 4, 4 * d->hidden_size);
+      return BLSTM_OK;
+    }
+    phase = BLSTM_PHASE_FWD;
+  }
   if (sm100_recurrence_supported(*d, phase)) {
     sm100_plan_detail(*d, phase, buf, buf_bytes);
   } else {
@@ -195,6 +207,11 @@ int blstm_fwd(const blstm_desc* d, const void* x, const void* h0, const void* c0
   } else {
     BLSTM_CUDA_OK(cudaMemsetAsync(out, 0, slot, st));
     BLSTM_CUDA_OK(cudaMemsetAsync(cell, 0, slot, st));
+  }
+  if (generic_fused_fwd_supported(*d)) {
+    // the kernel records nothing on the device, but callers read the control block afterwards
+    if (workspace && workspace_bytes >= sizeof(Control)) BLSTM_CUDA_OK(cudaMemsetAsync(workspace, 0, sizeof(Control), st));
+    return generic_fused_fwd(*d, x, Wx, Wh, bx, bh, ifgo, out, cell, st);
   }
   rc = blstm_input_projection(d, x, Wx, bx, bh, ifgo, stream);
   if (rc) return rc;

@@ -472,6 +472,131 @@ int generic_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh
   return BLSTM_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Tiny hidden sizes: the whole forward operator in ONE kernel (replaces
+// fully_fused_persistent_fwd_kernel, fastlstm/kernels.py:672-819, dispatch fastlstm/lstm.py:40-47).
+// With max(H, I) <= 32 (fp32) or <= 64 (16-bit) the input projection is as memory-bound as the
+// recurrence, so it is computed inside the time loop and the projected pre-activations never make a
+// round trip through memory.  A CTA owns FB batch rows and ALL 4H gate columns, so no CTA ever waits
+// for another: a plain launch, any batch size.  Thread n keeps row n of [Wx | Wh] (its gate column's
+// weights) in registers; per step the CTA stages [x_t | h_t] of its rows in shared memory, every
+// thread forms its column's pre-activation for the FB rows, and thread (row, unit) applies the gates
+// with c carried in a register.
+// ---------------------------------------------------------------------------
+constexpr int FB = 4;                   // batch rows per CTA
+
+template <typename T, int KMAX>         // KMAX >= I + H
+__global__ void __launch_bounds__(256)
+fused_fwd_kernel(int Tn, int B, int I, int H, int inference, const T* __restrict__ x, const T* __restrict__ Wx,
+                 const T* __restrict__ Wh, const T* __restrict__ bx, const T* __restrict__ bh,
+                 T* __restrict__ ifgo, T* __restrict__ out, T* __restrict__ cell) {
+  __shared__ __align__(16) float xh[FB][KMAX];          // [x_t | h_t] of the CTA's rows
+  __shared__ float pre[FB][256];                        // pre-activations, gate-major like ifgo
+  const int n = threadIdx.x, G = 4 * H, K = I + H;
+  const int row0 = blockIdx.x * FB;
+  float w[KMAX];
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) {
+    float v = 0.f;
+    if (n < G) {
+      if (k < I) v = ld_f(Wx + (size_t)n * I + k);
+      else if (k < K) v = ld_f(Wh + (size_t)n * H + (k - I));
+    }
+    w[k] = v;
+  }
+  // the bias as the unfused path forms it: bx + bh rounded to the storage type
+  float bias = 0.f;
+  if (n < G) bias = Elem<T>::to_f(Elem<T>::from_f((bx ? ld_f(bx + n) : 0.f) + (bh ? ld_f(bh + n) : 0.f)));
+  for (int i = n; i < FB * KMAX; i += blockDim.x) (&xh[0][0])[i] = 0.f;   // columns past K stay zero
+  __syncthreads();
+  // thread (rb, u) of the first FB*H threads owns one cell state
+  const int rb = n / H, u = n % H;
+  const bool owner = n < FB * H && row0 + rb < B;
+  float c = 0.f;
+  if (owner) {
+    c = ld_f(cell + (size_t)(row0 + rb) * H + u);
+    xh[rb][I + u] = ld_f(out + (size_t)(row0 + rb) * H + u);
+  } else if (n < FB * H) {
+    xh[rb][I + u] = 0.f;
+  }
+  for (int t = 0; t < Tn; ++t) {
+    for (int i = n; i < FB * I; i += blockDim.x) {
+      const int b = i / I, k = i % I;
+      xh[b][k] = (row0 + b < B) ? ld_f(x + ((size_t)t * B + row0 + b) * I + k) : 0.f;
+    }
+    __syncthreads();
+    float acc[FB];
+#pragma unroll
+    for (int b = 0; b < FB; ++b) acc[b] = bias;
+#pragma unroll
+    for (int k = 0; k < KMAX; k += 4) {
+      if (k < K) {
+#pragma unroll
+        for (int b = 0; b < FB; ++b) {
+          const float4 v = *reinterpret_cast<const float4*>(&xh[b][k]);
+          acc[b] = fmaf(w[k], v.x, acc[b]);
+          acc[b] = fmaf(w[k + 1], v.y, acc[b]);
+          acc[b] = fmaf(w[k + 2], v.z, acc[b]);
+          acc[b] = fmaf(w[k + 3], v.w, acc[b]);
+        }
+      }
+    }
+    if (n < G) {
+#pragma unroll
+      for (int b = 0; b < FB; ++b) {
+        pre[b][n] = acc[b];
+        if (!inference && row0 + b < B) ifgo[((size_t)t * B + row0 + b) * G + n] = Elem<T>::from_f(acc[b]);
+      }
+    }
+    __syncthreads();
+    if (owner) {
+      const float pi = pre[rb][u], pf = pre[rb][H + u], pg = pre[rb][2 * H + u], po = pre[rb][3 * H + u];
+      c = sigmoid_acc(pf) * c + sigmoid_acc(pi) * tanh_acc(pg);
+      const T h = Elem<T>::from_f(sigmoid_acc(po) * tanh_acc(c));
+      const size_t o1 = ((size_t)(t + 1) * B + row0 + rb) * H + u;
+      out[o1] = h;
+      if (!inference || t == Tn - 1) cell[o1] = Elem<T>::from_f(c);
+      xh[rb][I + u] = Elem<T>::to_f(h);                  // fed back at storage precision
+    }
+    // (the barrier at the top of the next step orders these writes before the next reads, and the x
+    //  columns written before it were last read before the barrier above)
+  }
+}
+
+bool generic_fused_fwd_supported(const blstm_desc& d) {
+  if (d.flags & BLSTM_FLAG_NO_FUSED) return false;
+  const int size = d.hidden_size > d.input_size ? d.hidden_size : d.input_size;
+  return size <= (d.dtype == BLSTM_F32 ? 32 : 64);
+}
+
+template <typename T>
+static int launch_fused(const blstm_desc& d, const void* x, const void* Wx, const void* Wh, const void* bx,
+                        const void* bh, void* ifgo, void* out, void* cell, cudaStream_t st) {
+  const int H = d.hidden_size, I = d.input_size;
+  const int threads = (int)round_up((size_t)(4 * H > FB * H ? 4 * H : FB * H), 32);
+  const int grid = cdiv(d.batch, FB);
+  const int inf = (d.flags & BLSTM_FLAG_INFERENCE) ? 1 : 0;
+  if (I + H <= 64)
+    fused_fwd_kernel<T, 64><<<grid, threads, 0, st>>>(d.seq_len, d.batch, I, H, inf, (const T*)x, (const T*)Wx, (const T*)Wh,
+                                                      (const T*)bx, (const T*)bh, (T*)ifgo, (T*)out, (T*)cell);
+  else
+    fused_fwd_kernel<T, 128><<<grid, threads, 0, st>>>(d.seq_len, d.batch, I, H, inf, (const T*)x, (const T*)Wx, (const T*)Wh,
+                                                       (const T*)bx, (const T*)bh, (T*)ifgo, (T*)out, (T*)cell);
+  BLSTM_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return BLSTM_OK;
+}
+
+int generic_fused_fwd(const blstm_desc& d, const void* x, const void* Wx, const void* Wh, const void* bx,
+                      const void* bh, void* ifgo, void* out, void* cell, cudaStream_t st) {
+  switch (d.dtype) {
+    case BLSTM_F32: return launch_fused<float>(d, x, Wx, Wh, bx, bh, ifgo, out, cell, st);
+    case BLSTM_F16: return launch_fused<__half>(d, x, Wx, Wh, bx, bh, ifgo, out, cell, st);
+    case BLSTM_BF16: return launch_fused<__nv_bfloat16>(d, x, Wx, Wh, bx, bh, ifgo, out, cell, st);
+  }
+  return BLSTM_E_INVALID_ARG;
+}
+
 // Column sums of d_ifgo [rows, cols]: part p adds the rows congruent to p modulo n_part, then
 // reduce_db adds the parts in a fixed order (deterministic).
 template <typename T>

@@ -31,6 +31,12 @@ int generic_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh
                            void* dh0, void* dc0, float* db, void* ws, size_t ws_bytes,
                            cudaStream_t st);
 
+// Whole forward operator in one kernel for tiny hidden sizes (max(H, I) <= 32 in fp32, <= 64 in 16 bit):
+// the input projection is computed inside the time loop.  out[0]/cell[0] must hold the initial state.
+bool generic_fused_fwd_supported(const blstm_desc& d);
+int generic_fused_fwd(const blstm_desc& d, const void* x, const void* Wx, const void* Wh, const void* bx,
+                      const void* bh, void* ifgo, void* out, void* cell, cudaStream_t st);
+
 int reduce_db(const float* part, int n_part, int n, float* db, cudaStream_t st);
 
 // db[4H] = column sums of d_ifgo [T*B,4H]; scratch = the backward recurrence workspace of this plan

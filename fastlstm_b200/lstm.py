@@ -125,10 +125,14 @@ def _after_launch(desc, ws, label):
         _status.poll(wait=False)
 
 
+_PHASES = {"fwd": _lib.PHASE_FWD, "bwd": _lib.PHASE_BWD, "fwd_op": _lib.PHASE_FWD_OP}
+
+
 def plan_name(dtype, T, B, I, H, phase="fwd"):
-    """Kernel family ("generic" / "sm100") the library picks for this problem."""
+    """Kernel family ("generic" / "sm100", for phase "fwd_op" also "fused") the library picks for this
+    problem.  Phases: "fwd" / "bwd" = the recurrences, "fwd_op" = the whole forward operator."""
     d = _desc(dtype, T, B, I, H)
-    return _lib.load().blstm_plan_name(d, _lib.PHASE_FWD if phase == "fwd" else _lib.PHASE_BWD).decode()
+    return _lib.load().blstm_plan_name(d, _PHASES[phase]).decode()
 
 
 def plan_detail(dtype, T, B, I, H, phase="fwd"):
@@ -136,8 +140,7 @@ def plan_detail(dtype, T, B, I, H, phase="fwd"):
     import ctypes
     d = _desc(dtype, T, B, I, H)
     buf = ctypes.create_string_buffer(512)
-    _lib.check(_lib.load().blstm_plan_detail(d, _lib.PHASE_FWD if phase == "fwd" else _lib.PHASE_BWD, buf, 512),
-               "blstm_plan_detail")
+    _lib.check(_lib.load().blstm_plan_detail(d, _PHASES[phase], buf, 512), "blstm_plan_detail")
     return buf.value.decode()
 
 
@@ -241,6 +244,48 @@ def Wgrad(d_ifgo, x, h):
     return db, db, dWx, dWh
 
 
+# ---------------------------------------------------------------------------
+# Ragged 16-bit shapes on the tensor-core kernels: TMA wants 16-byte row pitches (I % 8 == 0) and the
+# tcgen05 recurrences hidden sizes in multiples of 64.  Other shapes are zero-padded on the host: a padded
+# hidden unit has zero weights, bias and state, so its pre-activations are 0, its cell and output stay
+# exactly 0 and it feeds nothing into the real units; padded input columns meet zero weights.  The
+# padded copies cost a few small kernels per call - far less than the CUDA-core kernels they replace.
+# ---------------------------------------------------------------------------
+def _padded_sizes(dtype, I, H):
+    """(Ip, Hp) when the layer should run zero-padded on the tensor-core kernels, else None."""
+    if dtype not in (torch.float16, torch.bfloat16) or _FORCE_GENERIC:
+        return None
+    if max(I, H) <= 64:                       # tiny sizes have the fused kernel
+        return None
+    Ip, Hp = -(-I // 8) * 8, -(-H // 64) * 64
+    if (Ip, Hp) == (I, H) or Hp > 2048:
+        return None
+    return Ip, Hp
+
+
+def _pad_last(t, n):
+    return t if t is None or t.shape[-1] == n else torch.nn.functional.pad(t, (0, n - t.shape[-1]))
+
+
+def _pad_gates(W, H, Hp, cols=None):
+    """[4H, K] (or [4H]) -> [4Hp, cols or K]: every gate's block padded with zero rows (and columns)."""
+    if W is None:
+        return None
+    if W.dim() == 1:
+        return torch.nn.functional.pad(W.view(4, H), (0, Hp - H)).reshape(4 * Hp)
+    K = W.shape[1]
+    cols = K if cols is None else cols
+    return torch.nn.functional.pad(W.view(4, H, K), (0, cols - K, 0, Hp - H)).reshape(4 * Hp, cols)
+
+
+def _unpad_gates(G, H, Hp, cols=None):
+    """inverse of _pad_gates for gradients: [4Hp, Kp] -> [4H, cols]."""
+    if G.dim() == 1:
+        return G.view(4, Hp)[:, :H].reshape(4 * H)
+    cols = G.shape[1] if cols is None else cols
+    return G.view(4, Hp, G.shape[1])[:, :H, :cols].reshape(4 * H, cols)
+
+
 class PersistentLSTMfn(torch.autograd.Function):
     """autograd Function of one layer (fastlstm/lstm.py:504-538).
 
@@ -257,6 +302,15 @@ class PersistentLSTMfn(torch.autograd.Function):
             h_0 = None if h_0 is None else h_0.to(target)
             c_0 = None if c_0 is None else c_0.to(target)
         x = x.contiguous()
+        I, H = x.shape[-1], Wh.shape[1]
+        ctx.pad = _padded_sizes(x.dtype, I, H)
+        ctx.sizes = (I, H)
+        if ctx.pad is not None:
+            Ip, Hp = ctx.pad
+            x = _pad_last(x, Ip)
+            Wx, Wh = _pad_gates(Wx, H, Hp, Ip), _pad_gates(Wh, H, Hp, Hp)
+            bx, bh = _pad_gates(bx, H, Hp), _pad_gates(bh, H, Hp)
+            h_0, c_0 = _pad_last(h_0, Hp), _pad_last(c_0, Hp)
         # Grad mode is always off inside Function.forward and needs_input_grad mirrors requires_grad
         # whatever the grad mode, so the caller (persistent_lstm / FastLSTM.forward) decides whether
         # anything has to be saved; a bare apply() with the reference's seven arguments saves unless
@@ -272,6 +326,8 @@ class PersistentLSTMfn(torch.autograd.Function):
         ctx.h0_is_none = h_0 is None
         ctx.has_bias = (bx is not None, bh is not None)
         ctx.save_for_backward(x, out, cell, ifgo, Wx, Wh)
+        if ctx.pad is not None:
+            return out[1:, :, :H], out[-1, :, :H], cell[-1, :, :H]
         return out[1:], out[-1], cell[-1]
 
     @staticmethod
@@ -282,15 +338,33 @@ class PersistentLSTMfn(torch.autograd.Function):
         T, B, H = out.shape[0] - 1, out.shape[1], out.shape[2]
         if d_out is None:
             d_out = torch.zeros((T, B, H), device=x.device, dtype=x.dtype)
-        d_out = d_out.to(x.dtype).contiguous()
-        d_hn = None if d_hn is None else d_hn.to(x.dtype).contiguous()
-        d_cn = None if d_cn is None else d_cn.to(x.dtype).contiguous()
+        d_out = d_out.to(x.dtype)
+        d_hn = None if d_hn is None else d_hn.to(x.dtype)
+        d_cn = None if d_cn is None else d_cn.to(x.dtype)
+        if ctx.pad is not None:
+            d_out, d_hn, d_cn = _pad_last(d_out, H), _pad_last(d_hn, H), _pad_last(d_cn, H)   # H is the padded size here
+        d_out = d_out.contiguous()
+        d_hn = None if d_hn is None else d_hn.contiguous()
+        d_cn = None if d_cn is None else d_cn.contiguous()
         with torch.autograd.profiler.record_function("fastlstm_b200::bwd"):
             d_x, dh_0, dc_0, dWx, dbx, dWh, dbh = lstm_persistent_bwd(
                 d_out, d_cn, d_hn, x, out, cell, ifgo, Wx.contiguous(), Wh.contiguous(),
-                need_dx=ctx.needs_input_grad[0], wgrads=None if ctx.sink is None else ctx.sink.buffer)
+                need_dx=ctx.needs_input_grad[0],
+                wgrads=None if (ctx.sink is None or ctx.pad is not None) else ctx.sink.buffer)
+        if ctx.pad is not None:
+            I0, H0 = ctx.sizes
+            d_x = None if d_x is None else d_x[..., :I0]
+            dh_0, dc_0 = dh_0[:, :H0], dc_0[:, :H0]
+            dWx, dWh = _unpad_gates(dWx, H0, H, I0), _unpad_gates(dWh, H0, H, H0)
+            dbx = dbh = _unpad_gates(dbx, H0, H)
         if ctx.h0_is_none:
             dh_0 = dc_0 = None
+        if ctx.sink is not None and ctx.pad is not None:
+            # padded layer: the kernels wrote padded gradients, the bucket takes the unpadded ones
+            n1, n2 = dWx.numel(), dWx.numel() + dWh.numel()
+            ctx.sink.buffer[:n1].copy_(dWx.reshape(-1))
+            ctx.sink.buffer[n1:n2].copy_(dWh.reshape(-1))
+            ctx.sink.buffer[n2:].copy_(dbx)
         if ctx.sink is not None:
             # the fp32 gradients went straight into the caller's bucket segment: autograd sees none
             # (it would round them to the parameter dtype), the bucket hands them to p.grad later

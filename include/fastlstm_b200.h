@@ -56,6 +56,9 @@ enum {
                                    pre-activations nor cell[1..T-1] (nothing is saved for backward);
                                    out[1..T] and cell[T] are still produced.  Halves the bytes a
                                    step moves (5*B*H*e instead of 10*B*H*e). */
+  BLSTM_FLAG_NO_FUSED = 32,     /* blstm_fwd: do not use the single-kernel forward (projection inside the
+                                   time loop) that tiny sizes (max(H, I) <= 32 in fp32, <= 64 in 16 bit)
+                                   otherwise get; for comparisons and tests */
   BLSTM_FLAG_NO_CLUSTER = 16,   /* forward: do not use the cluster hand-off kernel that small hidden
                                    sizes (H = 64, 128, 256 with at most 7 batch tiles) otherwise get;
                                    for comparisons and tests */
@@ -75,7 +78,9 @@ typedef struct blstm_desc {
   int32_t reserved;
 } blstm_desc;
 
-enum { BLSTM_PHASE_FWD = 0, BLSTM_PHASE_BWD = 1 };
+/* BLSTM_PHASE_FWD_OP (plan queries only): the whole forward operator blstm_fwd, which for tiny sizes
+ * is one fused kernel ("fused") and otherwise projection + BLSTM_PHASE_FWD recurrence. */
+enum { BLSTM_PHASE_FWD = 0, BLSTM_PHASE_BWD = 1, BLSTM_PHASE_FWD_OP = 2 };
 
 /* ABI version of the loaded library (compare with BLSTM_ABI_VERSION). */
 int blstm_abi_version(void);
@@ -122,7 +127,9 @@ int blstm_fwd_recurrence(const blstm_desc* d, void* ifgo, const void* Wh, void* 
 
 /* Whole forward operator: initial-state slots, projection, recurrence.
  * h0/c0 [B,H] may both be NULL (zeros).  Replaces lstm_persistent_fwd,
- * fastlstm/lstm.py:31-146. */
+ * fastlstm/lstm.py:31-146, including its dispatch of tiny sizes to the fully fused kernel
+ * (fastlstm/lstm.py:40-47, fastlstm/kernels.py:672-819): one launch, no projected
+ * pre-activations in memory, no workspace use. */
 int blstm_fwd(const blstm_desc* d, const void* x, const void* h0, const void* c0,
               const void* Wx, const void* Wh, const void* bx, const void* bh,
               void* out, void* cell, void* ifgo,
