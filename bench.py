@@ -94,11 +94,16 @@ class ClockSampler(threading.Thread):
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-def workload_config(wl, cfg, world, seq_override=False):
+def workload_config(wl, cfg, world, seq_override=False, batch_override=False):
     """The keys that describe the workload; identical for every arm (ours, reference, cuDNN)."""
     es = ESIZE[cfg["dtype"]]
     B = cfg["B"]
-    return {"workload": wl if not seq_override else f"{wl} with T overridden to {cfg['T']} (profiling run, not the benchmark)",
+    name = wl
+    if seq_override:
+        name += f" with T overridden to {cfg['T']} (profiling run, not the benchmark)"
+    if batch_override:
+        name += f" with B overridden to {cfg['B']} (not the benchmark)"
+    return {"workload": name,
             "L": cfg["L"], "B": B, "B_per_gpu": B // world, "T": cfg["T"], "I": cfg["H"], "H": cfg["H"],
             "pass": "fwd+bwd" if cfg["bwd"] else "fwd", "sharding": f"batch/{world}",
             "l2": "inputs larger than L2 (no flush needed)" if (B // world) * cfg["T"] * cfg["H"] * es > 126e6
@@ -134,7 +139,7 @@ def run_reference(args, wl, cfg):
         "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(wl, cfg, max(1, args.gpus), args.seq_len > 0),
+        "config": workload_config(wl, cfg, max(1, args.gpus), args.seq_len > 0, args.batch > 0),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
@@ -195,10 +200,14 @@ def main():
                          "(default: only the final hidden state; the sequence and the gradients stay on the device)")
     ap.add_argument("--seq-len", type=int, default=0,
                     help="override T (profiling aid: shorter captures; the line then names the override)")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the global batch (e.g. 512 = one rank's share of c5 at 8 GPUs; the line names the override)")
     args = ap.parse_args()
     wl, cfg = args.workload, dict(WORKLOADS[args.workload])
     if args.seq_len > 0:
         cfg["T"] = args.seq_len
+    if args.batch > 0:
+        cfg["B"] = args.batch
     if args.impl == "reference":
         return run_reference(args, wl, cfg)
     args.warmup = max(args.warmup, 3)
@@ -263,7 +272,7 @@ def main():
             "value": L * Bg * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "ms_per_step_autocast": ms_ac, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
-            "config": workload_config(wl, cfg, 1, args.seq_len > 0),
+            "config": workload_config(wl, cfg, 1, args.seq_len > 0, args.batch > 0),
             "what": "torch.nn.LSTM (cuDNN), weights flattened",
             "clocks": sampler.result()}), flush=True)
         return
@@ -473,7 +482,7 @@ def main():
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": cfg["dtype"], "data": "synthetic",
-        "config": workload_config(wl, cfg, world, args.seq_len > 0),
+        "config": workload_config(wl, cfg, world, args.seq_len > 0, args.batch > 0),
         "collective": "fp32 sum-allreduce of dWx,dWh,db, one per layer, started from that layer's backward (NCCL)" if bucket is not None else "none",
         "plans": {"fwd": F.plan_detail(dt, T, B, H, H, "fwd"), "bwd": F.plan_detail(dt, T, B, H, H, "bwd")},
         "us_per_timestep": ms_step * 1e3 / (T * L),

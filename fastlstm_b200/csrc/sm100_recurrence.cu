@@ -193,7 +193,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   constexpr int EW = (UH == 16 && TI == 1) ? 4 : 8;
   constexpr int NU = 4 * UH / EW;                   // units per epilogue thread
   constexpr int NV = NU / 8;                        // 16-byte pieces per operand per thread
-  constexpr bool WRITER_FENCE = (TI == 1);          // which side runs the generic->async proxy fence
+  // Which side runs the generic->async proxy fence of the hand-off.  One tile in flight: the READER, after
+  // it has seen the counter (traced: the writers' release then waits for their h stores alone, 1.5 k clk
+  // instead of fence 1.8 k + release 1.5 k, against 0.8 k for the fence on the reading side).  Interleaved
+  // tiles: the writers' publisher warp.
+  constexpr bool WRITER_FENCE = false;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int H = p.H;
@@ -288,6 +292,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           // what lane 31 read for this item while the previous item's loads were being issued
           const int early_now = (TI >= 2) ? __shfl_sync(0xffffffffu, early, 31) : 0;
           if (TI >= 2) nx_valid = nx_valid && nx.next(pb, p.nb_par, p.nbt, n_chunks, p.T);
+          bool lane_ok = true;
+          // One tile in flight: the wait for each issuing lane's first ring stage (half a thousand clocks
+          // even when the stage is long free) is taken BEFORE the counter, off the step's chain.
+          const int kc_first = (lane + nacc - gs % nacc) % nacc;
+          if (TI == 1 && lane < nacc && kc_first < KC) {
+            int s = gs + kc_first;
+            uint32_t ph = gph;
+            while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
+            lane_ok = mbar_wait(&empty[s], ph ^ 1, wc);
+          }
           if (t > 0) {   // h[t] of this batch tile complete: every epilogue warp of every hidden tile arrived
             int seen = 1;
             if (lane == 0 && !(TI >= 2 && early_now >= p.flag_target)) {
@@ -297,20 +311,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             seen = __shfl_sync(0xffffffffu, seen, 0);
             if (!seen) { *dead = 1; ok = false; break; }
             // One proxy fence must lie between the peers' generic-proxy stores and this warp's TMA
-            // reads.  A single tile in flight is latency bound: the writers fence before their release
-            // (cheaper there).  With interleaved tiles neither the epilogue warps nor this warp can afford
-            // it (this loop then streams h without a break): the writers' publisher warp runs it.
+            // reads: here for a single tile in flight, in the writers' publisher warp otherwise (this
+            // loop then streams h without a break).
             if (!WRITER_FENCE && !PUBLISHER) fence_proxy_async();
           }
           const int row0 = bt * RB;
-          bool lane_ok = true;
-          if (lane < nacc) {
+          if (lane < nacc && lane_ok) {
             // this lane owns ring stages == lane (mod nacc): the item's chunks that land there
-            for (int kc = (lane + nacc - gs % nacc) % nacc; kc < KC; kc += nacc) {
+            for (int kc = kc_first; kc < KC; kc += nacc) {
               int s = gs + kc;
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
-              if (!mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
+              if (!(TI == 1 && kc == kc_first) && !mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
               tma_load_3d(a_s + (size_t)s * SB, &tmH, &full[s], kc * RK, row0, t);
               if (p.ws) tma_load_3d(a_s + (size_t)s * SB + R_STAGE_BYTES, &tmW, &full[s], kc * RK, ht * UH, 0);
             }
@@ -851,6 +863,7 @@ struct BwdParams {
   void* d_ifgo;             // [T,B,4H]
   void* dh0;                // [B,H]
   void* dc0;                // [B,H]
+  float* db_part;           // [nb_par * 4][4H] bias-gradient partial sums (one row per CTA group and row quarter), or null
 };
 
 template <typename T16>
@@ -880,7 +893,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   constexpr bool PUBLISHER = (TI >= 2);
   constexpr int N = 64, NACC = PUBLISHER ? 2 : 3, ACC_STRIDE = 256;   // NACC: MMA issuer warps
   constexpr int FIRST_EPI = 4;
-  constexpr bool WRITER_FENCE = (TI == 1);        // which side runs the generic->async proxy fence
+  constexpr bool WRITER_FENCE = false;            // the proxy fence of the hand-off: reader (one tile) or publisher warp
   constexpr int ITEM_WARPS = 8;                   // epilogue warps, all working on every item
   // Interleaved tiles are throughput bound and the epilogue's row-strided 16-byte global accesses were
   // the bottleneck there: the saved pre-activations come in, and d_ifgo goes out, as TMA boxes through
@@ -987,10 +1000,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           }
           seen = __shfl_sync(0xffffffffu, seen, 0);
           if (!seen) { *dead = 1; ok = false; break; }
-          // One proxy fence must lie between the peers' generic-proxy stores and the TMA reads below.
-          // A single tile in flight is latency bound: the writers fence before their release (cheaper
-          // there).  With interleaved tiles neither the epilogue warps nor this warp can afford it
-          // (this loop then streams d_ifgo without a break): the writers' publisher warp runs it.
+          // One proxy fence must lie between the peers' generic-proxy stores and the TMA reads below:
+          // here for a single tile in flight (the writers' release then waits for their stores alone),
+          // in the writers' publisher warp for interleaved tiles (this loop then streams without a break).
           if (!WRITER_FENCE && !PUBLISHER) fence_proxy_async();
           const int row0 = bt * RB, col0 = (int)r * H;
           bool lane_ok = true;
@@ -1130,6 +1142,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     const T16* dout = reinterpret_cast<const T16*>(p.dout);
     T16* dg = reinterpret_cast<T16*>(p.d_ifgo);
     const bool shipper = (warp == FIRST_EPI) && lane == 0;   // sends the staged slices
+    // Bias gradient (replaces the reduction of fastlstm/lstm.py:497 and a separate pass over d_ifgo):
+    // every thread adds the d_ifgo values it stores - as stored, i.e. rounded - to 32 fp32 sums of its
+    // own (4 gates x 8 units) that live in the tensor-memory columns behind the accumulators, one
+    // 32-column block per warpgroup; after the last step the 32 rows of a warp are added up with
+    // shuffles and lane 0 writes the warp's partial sums.
+    constexpr int DB_COL = 192;                  // NACC * N <= 192 columns per accumulator buffer are in use
+    const uint32_t db_taddr = tmem_base + DB_COL + g * 32 + (uint32_t(q * 32) << 16);
+    const bool want_db = p.db_part != nullptr;
+    if (want_db) {
+      uint32_t z[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) z[u] = 0u;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) tmem_st_32x8(db_taddr + 8 * k, z);
+      tmem_st_wait();
+    }
     int it = 0;                 // MMA items consumed so far: TMEM buffer it & 1, on its (it >> 1)-th use
     int pub_it = 0;             // gate-maths items published so far
     bool ok = true;
@@ -1415,6 +1443,23 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
                 qo[w] = pk2<T16>(r_[0][3], r_[1][3]);
               }
             }
+            if (want_db) {   // warp-uniform: tensor-memory loads and stores need the whole warp; rows past B add 0
+              const uint32_t* qs[4] = {qi, qf, qg, qo};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                uint32_t acc[8];
+                tmem_ld_32x8(db_taddr + 8 * k, acc);
+                tmem_ld_wait();
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                  const float2 f2 = cvt2<T16>(qs[k][w]);
+                  acc[2 * w] = __float_as_uint(__uint_as_float(acc[2 * w]) + (row_ok ? f2.x : 0.f));
+                  acc[2 * w + 1] = __float_as_uint(__uint_as_float(acc[2 * w + 1]) + (row_ok ? f2.y : 0.f));
+                }
+                tmem_st_32x8(db_taddr + 8 * k, acc);
+              }
+              tmem_st_wait();
+            }
             if constexpr (TMAEP) {
               // d_ifgo[t] goes back into the landing buffer the gates came from and leaves as one box.
               // The PREVIOUS item's box has been written by now: its buffer takes the gates of the item
@@ -1486,6 +1531,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     if (TMAEP && lane == 0) {
       tma_store_wait<0>();
       if (pending) { mbar_arrive(&pfree[(pub_it - 1) % 3]); mbar_arrive(&pub_bar[(pub_it - 1) & 3]); }
+    }
+    if (want_db) {
+      float* dst = p.db_part + ((size_t)pb * 4 + q) * H4 + unit0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        uint32_t acc[8];
+        tmem_ld_32x8(db_taddr + 8 * k, acc);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          float v = __uint_as_float(acc[u]);
+#pragma unroll
+          for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+          if (lane == 0) dst[(size_t)k * H + u] = v;
+        }
+      }
     }
   }
   // ---------------------------------------------------------------- teardown
@@ -1734,12 +1795,13 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   p.flags = reinterpret_cast<int*>(static_cast<char*>(ws) + pl.off_flags);
   p.dout = dout; p.dh_n = dh_n; p.dc_n = dc_n; p.ifgo = ifgo; p.cell = cell;
   p.d_ifgo = d_ifgo; p.dh0 = dh0; p.dc0 = dc0;
+  p.db_part = db ? reinterpret_cast<float*>(static_cast<char*>(ws) + pl.off_db) : nullptr;
   const bool bf = d.dtype == BLSTM_BF16;
   if (pl.TI == 1)      rc = bf ? launch_bwd_t<1, __nv_bfloat16>(pl, tw, tg, ti, td, p, st) : launch_bwd_t<1, __half>(pl, tw, tg, ti, td, p, st);
   else if (pl.TI == 2) rc = bf ? launch_bwd_t<2, __nv_bfloat16>(pl, tw, tg, ti, td, p, st) : launch_bwd_t<2, __half>(pl, tw, tg, ti, td, p, st);
   else                 rc = bf ? launch_bwd_t<4, __nv_bfloat16>(pl, tw, tg, ti, td, p, st) : launch_bwd_t<4, __half>(pl, tw, tg, ti, td, p, st);
   if (rc) return rc;
-  if (db) return sm100_bias_grad(d, d_ifgo, db, ws, ws_bytes, st);
+  if (db) return reduce_db(p.db_part, pl.nb_par * 4, 4 * H, db, st);   // the kernel left one row per CTA group and row quarter
   return BLSTM_OK;
 }
 
