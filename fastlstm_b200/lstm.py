@@ -293,7 +293,7 @@ class PersistentLSTMfn(torch.autograd.Function):
     unlike the reference, h_n and c_n are flat outputs and differentiable."""
 
     @staticmethod
-    def forward(ctx, x, h_0, c_0, Wx, bx, Wh, bh, inference=None, sink=None):
+    def forward(ctx, x, h_0, c_0, Wx, bx, Wh, bh, inference=None, sink=None, want_cells=False):
         if torch.is_autocast_enabled("cuda"):
             target = torch.get_autocast_dtype("cuda")
             x, Wx, Wh = x.to(target), Wx.to(target), Wh.to(target)
@@ -326,12 +326,18 @@ class PersistentLSTMfn(torch.autograd.Function):
         ctx.h0_is_none = h_0 is None
         ctx.has_bias = (bx is not None, bh is not None)
         ctx.save_for_backward(x, out, cell, ifgo, Wx, Wh)
-        if ctx.pad is not None:
-            return out[1:, :, :H], out[-1, :, :H], cell[-1, :, :H]
-        return out[1:], out[-1], cell[-1]
+        ctx.want_cells = bool(want_cells)
+        res = (out[1:, :, :H], out[-1, :, :H], cell[-1, :, :H]) if ctx.pad is not None else (out[1:], out[-1], cell[-1])
+        if want_cells:
+            # cell states of every step, for callers that need c at a step other than the last (packed
+            # sequences of different lengths); no gradient flows back through this output
+            cells = cell[1:, :, :H] if ctx.pad is not None else cell[1:]
+            ctx.mark_non_differentiable(cells)
+            return res + (cells,)
+        return res
 
     @staticmethod
-    def backward(ctx, d_out, d_hn, d_cn):
+    def backward(ctx, d_out, d_hn, d_cn, *_):
         if ctx.inference:
             raise RuntimeError("this forward ran in inference mode (nothing was saved); backward is not possible")
         x, out, cell, ifgo, Wx, Wh = ctx.saved_tensors
@@ -369,9 +375,9 @@ class PersistentLSTMfn(torch.autograd.Function):
             # the fp32 gradients went straight into the caller's bucket segment: autograd sees none
             # (it would round them to the parameter dtype), the bucket hands them to p.grad later
             ctx.sink.filled()
-            return (d_x, dh_0, dc_0, None, None, None, None, None, None)
+            return (d_x, dh_0, dc_0, None, None, None, None, None, None, None)
         return (d_x, dh_0, dc_0, dWx, dbx if ctx.has_bias[0] else None, dWh,
-                dbh if ctx.has_bias[1] else None, None, None)
+                dbh if ctx.has_bias[1] else None, None, None, None)
 
 
 def _nothing_to_save(*tensors):
@@ -398,7 +404,9 @@ class FastLSTM(nn.Module):
     Beyond the reference (which lists them as missing, README.md:92-93): `bidirectional` runs the
     same kernels on the time-reversed input and concatenates the two directions' outputs
     (states are ordered layer-major, direction-minor, like nn.LSTM); `dropout` is applied to
-    the outputs of every layer but the last while training.  `proj_size` is not implemented."""
+    the outputs of every layer but the last while training; a `PackedSequence` input gives a
+    `PackedSequence` output and the states at every sequence's own last step.  `proj_size` is not
+    implemented."""
 
     def __init__(self, input_size, hidden_size, num_layers=1, *, bias=True, batch_first=False,
                  version="persistent", device=None, dtype=None, dropout=0.0, bidirectional=False,
@@ -444,11 +452,46 @@ class FastLSTM(nn.Module):
         return g("weight_ih"), g("bias_ih"), g("weight_hh"), g("bias_hh")
 
     def forward(self, x, h_c_0=None):
+        if isinstance(x, torch.nn.utils.rnn.PackedSequence):
+            return self._forward_packed(x, h_c_0)
         if x.dim() != 3:
             raise ValueError("expected a 3-D input [T,B,I] (or [B,T,I] with batch_first)")
         if self.batch_first:
             x = x.transpose(0, 1)
+        return self._forward_padded(x, h_c_0, None)
+
+    def _forward_packed(self, seq, h_c_0):
+        """PackedSequence input (torch.nn.LSTM's convention; the reference lists it as missing,
+        README.md:92-93).  The sequences are padded to the longest, every layer runs over all T steps
+        (steps past a sequence's end compute values nobody reads - the recurrence is causal), the
+        final states are read at each sequence's own last step, and the output is packed again with
+        the input's ordering.  The reverse direction of a bidirectional layer walks every sequence
+        from its own end.  Gradients flow through the packed output and h_n; c_n of sequences shorter
+        than the longest carries no gradient."""
+        from torch.nn.utils.rnn import PackedSequence, pack_padded_sequence, pad_packed_sequence
+        x, lengths = pad_packed_sequence(seq, batch_first=False)          # [T,B,I], original batch order
+        out, states = self._forward_padded(x, h_c_0, lengths.to(x.device))
+        if seq.sorted_indices is not None:
+            out, lengths = out.index_select(1, seq.sorted_indices), lengths[seq.sorted_indices.cpu()]
+        data = pack_padded_sequence(out, lengths, enforce_sorted=True).data
+        return PackedSequence(data, seq.batch_sizes, seq.sorted_indices, seq.unsorted_indices), states
+
+    def _forward_padded(self, x, h_c_0, lengths):
+        """x [T,B,I]; lengths: None, or the [B] valid lengths (device tensor) of padded sequences."""
         nd = self.num_directions
+        T, B = x.shape[0], x.shape[1]
+        if lengths is not None:
+            steps = torch.arange(T, device=x.device)[:, None]                       # [T,1]
+            valid = steps < lengths[None, :]                                         # [T,B]
+            # per-sequence time reversal (identity past the end) and the index of the last valid step
+            rev = torch.where(valid, lengths[None, :] - 1 - steps, steps)            # [T,B]
+            last = (lengths - 1).clamp(min=0)                                        # [B]
+
+            def reverse_time(t):
+                return t.gather(0, rev[:, :, None].expand(-1, -1, t.shape[2]))
+
+            def at_last(t):                                                          # [T,B,H] -> [B,H]
+                return t.gather(0, last[None, :, None].expand(1, -1, t.shape[2]))[0]
         if h_c_0 is None:
             h_0 = c_0 = [None] * (self.num_layers * nd)
         else:
@@ -463,17 +506,23 @@ class FastLSTM(nn.Module):
             outs = []
             for d in range(nd):
                 Wx, bx, Wh, bh = self.layer_params(layer, reverse=(d == 1))
-                x_d = x.flip(0) if d == 1 else x          # the reverse direction walks t = T-1 .. 0
+                # the reverse direction walks t = T-1 .. 0 (every sequence from its own end when packed)
+                x_d = x if d == 0 else (x.flip(0) if lengths is None else reverse_time(x))
                 hl, cl = h_0[layer * nd + d], c_0[layer * nd + d]
                 inference = _nothing_to_save(x_d, hl, cl, Wx, bx, Wh, bh)
                 sink = None if self._sinks is None else self._sinks[layer * nd + d]
-                o, h_i, c_i = PersistentLSTMfn.apply(x_d, hl, cl, Wx, bx, Wh, bh, inference, sink)
-                outs.append(o.flip(0) if d == 1 else o)
+                if lengths is None:
+                    o, h_i, c_i = PersistentLSTMfn.apply(x_d, hl, cl, Wx, bx, Wh, bh, inference, sink)
+                else:
+                    o, _, _, cells = PersistentLSTMfn.apply(x_d, hl, cl, Wx, bx, Wh, bh, inference, sink, True)
+                    h_i, c_i = at_last(o), at_last(cells)      # states at each sequence's own last step
+                    o = o * valid[:, :, None].to(o.dtype)      # steps past the end read as zeros
+                outs.append(o if d == 0 else (o.flip(0) if lengths is None else reverse_time(o)))
                 h_n.append(h_i)
                 c_n.append(c_i)
             x = outs[0] if nd == 1 else torch.cat(outs, dim=-1)
             if self.dropout > 0.0 and self.training and layer < self.num_layers - 1:
                 x = torch.nn.functional.dropout(x, self.dropout, True)
-        if self.batch_first:
+        if self.batch_first and lengths is None:
             x = x.transpose(0, 1)
         return x, (torch.stack(h_n), torch.stack(c_n))

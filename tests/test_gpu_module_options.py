@@ -100,3 +100,48 @@ def test_dropout_only_acts_between_layers_while_training():
     one.train()
     assert torch.equal(one(x)[0], one(x)[0])                     # a single layer has nothing to drop
     F.check_status()
+
+
+@pytest.mark.parametrize("dtype,bidirectional,H", [("fp32", False, 24), ("fp32", True, 40), ("bf16", True, 128)])
+def test_packed_sequence_matches_nn_lstm(dtype, bidirectional, H):
+    """PackedSequence input (sequences of different lengths, unsorted): packed output, states at every
+    sequence's own last step, the reverse direction from every sequence's own end, and the gradients
+    through the output and h_n, against torch.nn.LSTM float64 on the CPU."""
+    import fastlstm_b200 as F
+    from torch.nn.utils.rnn import pack_padded_sequence
+    I, L, B, T = 12, 2, 6, 9
+    m, ref = _pair(I, H, L, dtype, seed=21, bidirectional=bidirectional)
+    dt = TORCH_DT[dtype]
+    nd = 2 if bidirectional else 1
+    g = torch.Generator().manual_seed(22)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(dt).double()
+    x = rnd(T, B, I)
+    lengths = torch.tensor([4, 9, 1, 6, 9, 2])
+    h0, c0 = rnd(L * nd, B, H) * 0.1, rnd(L * nd, B, H) * 0.1
+    h0, c0 = h0.to(dt).double(), c0.to(dt).double()
+
+    def go(mod, cast):
+        xi = cast(x).requires_grad_(True)
+        out, (hn, cn) = mod(pack_padded_sequence(xi, lengths, enforce_sorted=False), (cast(h0), cast(c0)))
+        (out.data.float().square().sum() + hn.float().sum()).backward()
+        f = lambda t: t.detach().double().cpu().numpy()
+        res = {"out": f(out.data), "h_n": f(hn), "c_n": f(cn), "dx": f(xi.grad), "bs": out.batch_sizes.clone()}
+        for n, p in mod.named_parameters():
+            res["grad:" + n] = f(p.grad)
+        return res
+
+    got = go(m, lambda t: t.to("cuda", dt))
+    want = go(ref, lambda t: t.clone())
+    torch.cuda.synchronize()
+    F.check_status()
+    assert torch.equal(got["bs"], want["bs"])
+    for k in want:
+        if k == "bs":
+            continue
+        if dtype == "fp32":
+            assert max_rel(got[k], want[k]) <= 2e-5, k
+        elif k in ("out", "h_n", "c_n"):
+            assert float(np.max(np.abs(got[k] - want[k]))) <= 2e-2, k
+        else:
+            e = float(np.linalg.norm(got[k] - want[k]) / max(np.linalg.norm(want[k]), 1e-30))
+            assert e <= 5e-2, (k, e)

@@ -51,3 +51,57 @@ def test_bidirectional_parameters_match_nn_lstm_and_options_are_validated():
         FastLSTM(4, 4, proj_size=2)
     with pytest.raises(ValueError):
         FastLSTM(4, 4, dropout=1.5)
+
+
+class _TorchLayer:
+    """Stand-in for PersistentLSTMfn on CPU: the same call signature, plain differentiable torch ops."""
+
+    @staticmethod
+    def apply(x, h0, c0, Wx, bx, Wh, bh, inference=None, sink=None, want_cells=False):
+        T, B, _ = x.shape
+        H = Wh.shape[1]
+        h = x.new_zeros(B, H) if h0 is None else h0
+        c = x.new_zeros(B, H) if c0 is None else c0
+        outs, cells = [], []
+        for t in range(T):
+            a = x[t] @ Wx.T + h @ Wh.T + (0 if bx is None else bx + bh)
+            i, f, g, o = a.split(H, dim=1)
+            c = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(g)
+            h = torch.sigmoid(o) * torch.tanh(c)
+            outs.append(h)
+            cells.append(c)
+        out = torch.stack(outs)
+        res = (out, out[-1], cells[-1])
+        return res + (torch.stack(cells).detach(),) if want_cells else res
+
+
+@pytest.mark.parametrize("bidirectional", [False, True])
+def test_packed_sequence_plumbing_matches_nn_lstm(monkeypatch, bidirectional):
+    """PackedSequence in, PackedSequence out, states at every sequence's own last step, the reverse
+    direction from every sequence's own end, gradients through the packed output and h_n - checked on
+    CPU with a torch stand-in for the CUDA layer against torch.nn.LSTM."""
+    import fastlstm_b200.lstm as mod
+    from torch.nn.utils.rnn import pack_padded_sequence
+    monkeypatch.setattr(mod, "PersistentLSTMfn", _TorchLayer)
+    torch.manual_seed(4)
+    I, H, L = 5, 6, 2
+    ref = torch.nn.LSTM(I, H, num_layers=L, bidirectional=bidirectional).double()
+    m = mod.FastLSTM(I, H, num_layers=L, bidirectional=bidirectional, dtype=torch.float64)
+    m.load_state_dict(ref.state_dict())
+    lengths = torch.tensor([3, 7, 1, 5])
+    x = torch.randn(7, 4, I, dtype=torch.float64)
+    nd = 2 if bidirectional else 1
+    h0, c0 = torch.randn(L * nd, 4, H, dtype=torch.float64), torch.randn(L * nd, 4, H, dtype=torch.float64)
+    results = []
+    for net in (ref, m):
+        xi = x.clone().requires_grad_()
+        out, (hn, cn) = net(pack_padded_sequence(xi, lengths, enforce_sorted=False), (h0, c0))
+        (out.data.square().sum() + hn.sum()).backward()
+        results.append((out, hn, cn, xi.grad, [p.grad.clone() for p in net.parameters()]))
+        net.zero_grad()
+    (o1, h1, c1, g1, p1), (o2, h2, c2, g2, p2) = results
+    assert torch.equal(o1.batch_sizes, o2.batch_sizes) and torch.equal(o1.sorted_indices, o2.sorted_indices)
+    for a, b in ((o1.data, o2.data), (h1, h2), (c1, c2), (g1, g2)):
+        torch.testing.assert_close(a, b, rtol=1e-9, atol=1e-10)
+    for a, b in zip(p1, p2):
+        torch.testing.assert_close(a, b, rtol=1e-9, atol=1e-10)
