@@ -33,8 +33,8 @@ namespace sm100 {
 
 constexpr int RB = 128;                 // batch rows per tile (MMA M)
 constexpr int RK = 64;                  // K chunk (one 128-byte swizzle row)
-constexpr int R_MAX_STAGES = 8;
-constexpr int R_STAGE_BYTES = RB * RK * 2;   // 16 KB
+constexpr int R_MAX_STAGES = 16;
+constexpr int R_STAGE_BYTES = RB * RK * 2;   // 16 KB: what an M = 128 MMA reads of a stage's activation rows
 
 // Ring depth R and number of concurrent TMA-issuing lanes / MMA-issuing warps NI.  Every stage
 // barrier must always be waited on by the SAME thread of each role (a parity wait cannot tell
@@ -46,9 +46,9 @@ static bool pick_ring(size_t fixed_bytes, size_t stage_bytes, int max_ni, int kc
   // Prefer many concurrent issuers, but only count them fully when the ring holds two rounds of
   // their chunks (R >= 2 NI): with R == NI the loads of one round cannot overlap the MMAs of the
   // previous one.
-  const int cand[5] = {8, 6, 4, 3, 2};
+  const int cand[7] = {16, 12, 8, 6, 4, 3, 2};
   int best_r = 0, best_n = 0, best_score = -1;
-  for (int i = 0; i < 5; ++i) {
+  for (int i = 0; i < 7; ++i) {
     const int r = cand[i];
     if (fixed_bytes + (size_t)r * stage_bytes > 232448) continue;
     for (int n = 4; n >= 1; --n) {
@@ -67,6 +67,8 @@ struct RecPlan {
   bool ok;
   int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages, ni, ws;
   int npb;                  // interleaved tiles: TMA landing buffers per epilogue warp (1 or 2), else 0
+  int kr;                   // K chunks of the Wh slice that stay resident (all of them unless ws)
+  int hb;                   // bytes of the h rows in a ring stage: 128 rows, or a single smaller tile's own rows
   size_t w_bytes, stage_bytes, smem, ep_bytes;
   size_t off_flags, n_flags, ws_bytes;
 };
@@ -103,11 +105,22 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   const int n_issuers = (UH == 16 && p.TI == 1) ? 4 : (UH == 32 && p.TI >= 2) ? 1 : 2;
   const int n_publisher = p.TI >= 2 ? 1 : 0;
   p.threads = 32 * (1 + n_issuers + n_publisher + p.epi_warps);   // producer + MMA issuers [+ publisher] + epilogue
-  // Wh slice resident in shared memory when it fits next to a useful ring; otherwise (H > 1024)
-  // the slice is streamed through the ring with h, chunk by chunk, every step (it stays in L2)
+  // Wh slice resident in shared memory when it fits next to a useful ring; otherwise (H > 1024) it is
+  // streamed through the ring with h, chunk by chunk, every step (it stays in L2).  A single batch tile
+  // of fewer than 128 rows only stages its own rows (the MMA's rows past them read whatever follows:
+  // accumulator rows nobody uses), which makes room for up to 16 stages.
   p.w_bytes = (size_t)p.N * H * 2;
   p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;
-  p.stage_bytes = R_STAGE_BYTES + (p.ws ? (size_t)p.N * 128 : 0);
+  p.hb = (p.nbt == 1 ? (int)round_up((size_t)B, 8) : RB) * 128;
+  const size_t w_chunk = (size_t)p.N * 128;
+  p.stage_bytes = p.hb + (p.ws ? w_chunk : 0);
+  // (a stage that holds fewer than 128 rows is still READ as 128 rows by the MMA: the ring is followed by
+  //  enough shared memory for the last stage's read to stay inside the allocation)
+  const size_t tail_pad = p.stage_bytes < (size_t)R_STAGE_BYTES ? R_STAGE_BYTES - p.stage_bytes : 0;
+  // Streamed means ALL of it: keeping 18 of H=2048's 32 chunks resident (6-stage ring) measured 10.2 ms
+  // against 8.1 ms with none resident and a 16-stage ring - the depth of the ring is worth more than
+  // the bytes saved.  (The kernel handles any split; `kr` chunks are resident.)
+  p.kr = p.ws ? 0 : H / RK;
   // Interleaved tiles: the epilogue's gate traffic goes through TMA.  Every epilogue warp owns
   // landing buffers for its 32 rows' projected pre-activations (4 gates x NU units; the final
   // pre-activations are written back in place and stored from there).
@@ -115,7 +128,7 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   // still gets four stages, else one.
   p.npb = 0;
   p.ep_bytes = 0;
-  size_t fixed = 1024 + (p.ws ? 0 : p.w_bytes) + 512;
+  size_t fixed = 1024 + (size_t)p.kr * w_chunk + 512 + tail_pad;
   if (p.TI >= 2) {
     const int NU = 4 * UH / p.epi_warps;
     const size_t pb = 256 * (size_t)NU;
@@ -137,7 +150,9 @@ struct FwdParams {
   int nbt, nh, nb_par, ntl;
   int stages;
   int ni;                   // TMA-issuing lanes = MMA-issuing warps in use
-  int ws;                   // 1: Wh slice streamed through the ring instead of resident
+  int ws;                   // 1: part of the Wh slice streamed through the ring instead of resident
+  int kr;                   // resident K chunks of the Wh slice
+  int hb;                   // bytes of the h rows in a ring stage
   int stage_bytes;
   int fmt;
   int no_arrive;
@@ -205,7 +220,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint8_t* w_s = smem;                              // [KC][N rows][128 B]
   const int R_STAGES = p.stages;
   const int SB = p.stage_bytes;                     // h chunk (16 KB) [+ Wh chunk when streamed]
-  uint8_t* ep_s = smem + (p.ws ? 0 : (size_t)N * H * 2);  // epilogue TMA buffers (interleaved tiles)
+  uint8_t* ep_s = smem + (size_t)p.kr * N * 128;          // epilogue TMA buffers (interleaved tiles)
+  const int HB = p.hb;                                    // h rows of a stage; a streamed Wh chunk follows them
   uint8_t* a_s = ep_s + p.ep_bytes;                       // [stages][h chunk | optional Wh chunk]
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;                            // [R_MAX_STAGES]
@@ -249,7 +265,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], EW);
     for (int i = 0; i < 16; ++i) mbar_init(&pre_full[i], 1);
     fence_mbar_init();
-    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
+    // (stage s is first used by chunk s; with streamed weights there are more chunks than stages)
+    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], (p.ws && s % KC >= p.kr) ? SB : HB);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmH);
     if (TMAEP) tma_prefetch_desc(&tmP);
@@ -269,10 +286,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     // ---------------------------------------------------------------- TMA producer
     // One thread needs a few hundred clocks per cp.async.bulk.tensor issue, so p.ni lanes issue in
     // lockstep, each owning the ring stages congruent to its lane index.
-    if (lane == 0 && !p.ws) {
-      // resident Wh slice: rows (gate g, unit ht*UH + u), all K, as KC chunks of [N][64]
-      mbar_expect_tx(w_full, (uint32_t)((size_t)N * H * 2));
-      for (int kc = 0; kc < KC; ++kc) tma_load_3d(w_s + (size_t)kc * N * 128, &tmW, w_full, kc * RK, ht * UH, 0);
+    if (lane == 0 && p.kr > 0) {
+      // resident part of the Wh slice: rows (gate g, unit ht*UH + u), K chunks [0, kr) of [N][64]
+      mbar_expect_tx(w_full, (uint32_t)((size_t)p.kr * N * 128));
+      for (int kc = 0; kc < p.kr; ++kc) tma_load_3d(w_s + (size_t)kc * N * 128, &tmW, w_full, kc * RK, ht * UH, 0);
     }
     int gs = 0;                // ring position of the current item's chunk 0
     uint32_t gph = 0;
@@ -324,7 +341,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!(TI == 1 && kc == kc_first) && !mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
               tma_load_3d(a_s + (size_t)s * SB, &tmH, &full[s], kc * RK, row0, t);
-              if (p.ws) tma_load_3d(a_s + (size_t)s * SB + R_STAGE_BYTES, &tmW, &full[s], kc * RK, ht * UH, 0);
+              if (kc >= p.kr) tma_load_3d(a_s + (size_t)s * SB + HB, &tmW, &full[s], kc * RK, ht * UH, 0);
             }
           } else if (TI >= 2 && lane == 31) {
             // (the other arm of the same branch: the issuing lanes do not wait for this read)
@@ -370,7 +387,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       // Every tcgen05 instruction (mma or commit) costs this thread ~150 clocks of issue time, so
       // issuer x owns WHOLE chunks (kc = x, x+NACC, ...): four MMAs and one commit per chunk,
       // in parallel with the other issuers, each into its own accumulator.
-      bool ok = (x < nacc) && (p.ws || mbar_wait(w_full, 0, wc));
+      bool ok = (x < nacc) && (p.kr == 0 || mbar_wait(w_full, 0, wc));
       int gs = 0;
       uint32_t gph = 0;
       uint32_t acc_ph[2] = {0, 0};
@@ -393,10 +410,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait_spin(&full[s], ph, wc)) { ok = false; break; }
-              mbar_expect_tx(&full[s], SB);   // arm the stage's next use
+              // arm the stage's next use: R_STAGES chunks further on (chunks wrap around within an item)
+              mbar_expect_tx(&full[s], (p.ws && (kc + R_STAGES) % KC >= p.kr) ? SB : HB);
               tc_fence_after();
               const uint32_t sa = smem_u32(a_s + (size_t)s * SB);
-              const uint32_t sb = p.ws ? sa + R_STAGE_BYTES : w_addr + (uint32_t)kc * N * 128;
+              const uint32_t sb = kc >= p.kr ? sa + HB : w_addr + (uint32_t)kc * N * 128;
 #pragma unroll
               for (int k = 0; k < RK / 16; ++k)
                 umma_f16(d_tmem, smem_desc(descK, sa + k * 32), smem_desc(descK, sb + k * 32), idesc,
@@ -771,6 +789,8 @@ constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x
 struct BwdPlan {
   bool ok;
   int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni, ws, alias;
+  int kr;                   // K chunks of the Wh slice that stay resident (all of them unless ws)
+  int hb;                   // bytes of the d_ifgo rows in a ring stage (128 rows, or a single smaller tile's own)
   size_t w_bytes, recv_bytes, stage_bytes, smem, ep_bytes;
   size_t off_flags, n_flags, off_db, ws_bytes;
 };
@@ -797,8 +817,16 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.threads = 0;                          // set below
   p.w_bytes = (size_t)H * 128;
   p.ws = p.w_bytes > 128 * 1024 ? 1 : 0;                   // stream the Wh slice through the ring
-  p.stage_bytes = R_STAGE_BYTES + (p.ws ? 8192 : 0);
-  const size_t wres = p.ws ? 0 : p.w_bytes;
+  p.hb = (p.nbt == 1 ? (int)round_up((size_t)B, 8) : RB) * 128;
+  p.stage_bytes = p.hb + (p.ws ? 8192 : 0);
+  const int KCp = H / RK;
+  // (a stage that holds fewer than 128 rows is still READ as 128 rows by the MMA: the ring is followed by
+  //  enough shared memory for the last stage's read to stay inside the allocation)
+  const size_t tail_pad = p.stage_bytes < (size_t)R_STAGE_BYTES ? R_STAGE_BYTES - p.stage_bytes : 0;
+  // Streamed means all of it (the depth of the ring is worth more than the bytes a resident part saves:
+  // H=2048 measured 12.5 ms with 18 of 32 chunks resident against 11.5 ms with none); the kernel handles
+  // any split, `kr` chunks are resident.
+  auto resident_chunks = [&](size_t) { return p.ws ? 0 : KCp; };
   // Cluster exchange: receive slots (3 peers x 8 KB) and send staging (3 x 8 KB), one set.  With
   // interleaved tiles a CTA tells its three peers when it has consumed an item's slices, and nobody
   // stages or ships the next item before all three have said so (`consumed` in the kernel).
@@ -806,11 +834,14 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   // epilogue warp (32 rows x 4 gates x 8 units; d_ifgo is written back in place and stored from there).
   p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
   p.ep_bytes = p.TI >= 2 ? (size_t)8 * 3 * 2048 : 0;
-  if (1024 + wres + p.recv_bytes + p.ep_bytes + 1024 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
+  p.kr = resident_chunks(1024 + p.recv_bytes + p.ep_bytes + 1024);
+  if (1024 + (size_t)p.kr * 8192 + p.recv_bytes + p.ep_bytes + 1024 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
     p.TI = 1;                                               // not enough room to interleave tiles
     p.ep_bytes = 0;
+    p.kr = resident_chunks(1024 + p.recv_bytes + 1024);
   }
-  size_t fixed = 1024 + wres + p.recv_bytes + p.ep_bytes + 1024;  // 1024: barriers and counters behind the ring
+  size_t wres = (size_t)p.kr * 8192;
+  size_t fixed = 1024 + wres + p.recv_bytes + p.ep_bytes + 1024 + tail_pad;  // 1024: barriers and counters behind the ring
   // warps: 1 producer + 3 MMA issuers (or 2 + a publisher warp when tiles are interleaved) + 2 epilogue
   // warpgroups = 12 (3 per SM sub-partition, 168 registers each); a 13th warp would cap every thread
   // at 128 registers.
@@ -824,7 +855,7 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.alias = 0;
   if (p.TI == 1 && p.stages < 6) {
     int st2 = 0, ni2 = 0;
-    const size_t fixed2 = 1024 + wres + 1024;
+    const size_t fixed2 = 1024 + wres + 1024 + tail_pad;
     if (pick_ring(fixed2, p.stage_bytes, n_issuers, H / RK, &st2, &ni2) && st2 > p.stages &&
         (size_t)st2 * p.stage_bytes >= p.recv_bytes) {
       p.alias = 1; p.stages = st2; p.ni = ni2; fixed = fixed2;
@@ -845,6 +876,8 @@ struct BwdParams {
   int stages;
   int ni;
   int ws;
+  int kr;                   // resident K chunks of the Wh slice
+  int hb;                   // bytes of the d_ifgo rows in a ring stage
   int stage_bytes;
   int fmt;
   int no_arrive;
@@ -908,7 +941,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   const int R_STAGES = p.stages;
   uint8_t* w_s = smem;                                        // [KC][64 k rows][128 B]
   const int SB = p.stage_bytes;                               // d_ifgo chunk (16 KB) [+ Wh chunk when streamed]
-  uint8_t* recv = smem + (p.ws ? 0 : (size_t)H * 128);                     // [3 senders][128 rows][64 B]
+  const int HB = p.hb;                                        // d_ifgo rows of a stage; a streamed Wh chunk follows
+  uint8_t* recv = smem + (size_t)p.kr * 8192;                 // [3 senders][128 rows][64 B]
   constexpr int XB = 1;                                       // one set of exchange buffers
   uint8_t* stage = recv + (size_t)XB * 3 * XSLOT_BYTES;      // [3 receivers][128 rows][64 B]
   uint8_t* ep_s = stage + (size_t)XB * 3 * XSLOT_BYTES;      // epilogue TMA buffers [8 warps][3][2 KB]
@@ -951,7 +985,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     mbar_init(consumed, 3 * ITEM_WARPS);
     for (int i = 0; i < 24; ++i) { mbar_init(&pre_full[i], 1); mbar_init(&pre_free[i], 1); }
     fence_mbar_init();
-    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], SB);
+    for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], (p.ws && s % KC >= p.kr) ? SB : HB);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmG);
     if (TMAEP) { tma_prefetch_desc(&tmI); tma_prefetch_desc(&tmD); }
@@ -970,9 +1004,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   // dh = d_ifgo[T-s] x Wh for its tile, then (s < T) does the gate maths of step t = T-1-s.
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0 && !p.ws) {
-      mbar_expect_tx(w_full, (uint32_t)((size_t)H * 128));
-      for (int kc = 0; kc < KC; ++kc)
+    if (lane == 0 && p.kr > 0) {
+      mbar_expect_tx(w_full, (uint32_t)((size_t)p.kr * 8192));
+      for (int kc = 0; kc < p.kr; ++kc)
         tma_load_2d(w_s + (size_t)kc * 8192, &tmW, w_full, ugc * 64, (int)r * H + kc * RK);
     }
     int gs = 0;
@@ -1014,7 +1048,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait(&empty[s], ph ^ 1, wc)) { lane_ok = false; break; }
               tma_load_3d(a_s + (size_t)s * SB, &tmG, &full[s], col0 + kc * RK, row0, tg);
-              if (p.ws) tma_load_2d(a_s + (size_t)s * SB + R_STAGE_BYTES, &tmW, &full[s], ugc * 64, col0 + kc * RK);
+              if (kc >= p.kr) tma_load_2d(a_s + (size_t)s * SB + HB, &tmW, &full[s], ugc * 64, col0 + kc * RK);
             }
           } else if (TI >= 2 && lane == 31) {
             // (the other arm of the same branch: the issuing lanes do not wait for this read)
@@ -1084,7 +1118,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       constexpr uint64_t descA = smem_desc_base(16, 1024);       // d_ifgo tile, K-major
       constexpr uint64_t descB = smem_desc_base(8192, 1024);     // Wh chunk, N-major (64 units wide)
       const uint32_t idesc = instr_desc(p.fmt, 0, 1, RB, N);
-      bool ok = (x < nacc) && (p.ws || mbar_wait(w_full, 0, wc));
+      bool ok = (x < nacc) && (p.kr == 0 || mbar_wait(w_full, 0, wc));
       int gs = 0;
       uint32_t gph = 0;
       uint32_t acc_ph[2] = {0, 0};
@@ -1107,10 +1141,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
               if (!mbar_wait_spin(&full[s], ph, wc)) { ok = false; break; }
-              mbar_expect_tx(&full[s], SB);   // arm the stage's next use
+              // arm the stage's next use: R_STAGES chunks further on (chunks wrap around within an item)
+              mbar_expect_tx(&full[s], (p.ws && (kc + R_STAGES) % KC >= p.kr) ? SB : HB);
               tc_fence_after();
               const uint32_t sa = smem_u32(a_s + (size_t)s * SB);
-              const uint32_t sb = p.ws ? sa + R_STAGE_BYTES : w_addr + (uint32_t)kc * 8192;
+              const uint32_t sb = kc >= p.kr ? sa + HB : w_addr + (uint32_t)kc * 8192;
 #pragma unroll
               for (int k = 0; k < RK / 16; ++k)
                 umma_f16(d_tmem, smem_desc(descA, sa + k * 32), smem_desc(descB, sb + k * 2048), idesc,
@@ -1648,17 +1683,23 @@ int sm100_plan_detail(const blstm_desc& d, int phase, char* buf, size_t n) {
   if (phase == BLSTM_PHASE_BWD) {
     const BwdPlan p = make_bwd_plan(d);
     if (!p.ok) return 0;
+    char wh[48];
+    if (p.ws) snprintf(wh, sizeof(wh), "%d/%d chunks resident, rest streamed", p.kr, d.hidden_size / RK);
+    else snprintf(wh, sizeof(wh), "resident");
     return snprintf(buf, n, "sm100 bwd cluster=4 units_per_cluster=64 TI=%d grid=%d threads=%d stages=%d issuers=%d "
-                    "wh=%s alias=%d smem=%zu", p.TI, p.grid, p.threads, p.stages, p.ni,
-                    p.ws ? "streamed" : "resident", p.alias, p.smem);
+                    "rows_per_stage=%d wh=%s alias=%d smem=%zu", p.TI, p.grid, p.threads, p.stages, p.ni, p.hb / 128, wh,
+                    p.alias, p.smem);
   }
   const RecPlan p = make_plan(d, phase);
   if (!p.ok) return 0;
   if (sm100_fwd_cluster_shape(d))
     return snprintf(buf, n, "sm100 fwd cluster=%d (one per batch tile, h handed over in shared memory) UH=16 TI=1 grid=%d "
                     "threads=288 wh=resident", d.hidden_size / 16, d.hidden_size / 16 * p.nbt);
-  return snprintf(buf, n, "sm100 fwd UH=%d TI=%d grid=%d threads=%d stages=%d issuers=%d wh=%s smem=%zu", p.UH, p.TI,
-                  p.grid, p.threads, p.stages, p.ni, p.ws ? "streamed" : "resident", p.smem);
+  char wh[48];
+  if (p.ws) snprintf(wh, sizeof(wh), "%d/%d chunks resident, rest streamed", p.kr, d.hidden_size / RK);
+  else snprintf(wh, sizeof(wh), "resident");
+  return snprintf(buf, n, "sm100 fwd UH=%d TI=%d grid=%d threads=%d stages=%d issuers=%d rows_per_stage=%d wh=%s smem=%zu",
+                  p.UH, p.TI, p.grid, p.threads, p.stages, p.ni, p.hb / 128, wh, p.smem);
 }
 
 int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* out, void* cell, void* ws,
@@ -1682,7 +1723,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   {  // out [T+1,B,H] as {k, batch row, t}: rows past B are zero-filled, never another timestep
     uint64_t dims[3] = {(uint64_t)H, (uint64_t)B, (uint64_t)(T + 1)};
     uint64_t str[2] = {(uint64_t)H * 2, (uint64_t)B * H * 2};
-    uint32_t box[3] = {RK, RB, 1};
+    uint32_t box[3] = {RK, (uint32_t)(pl.hb / 128), 1};
     rc = encode_tensor_map(&th, out, 3, dims, str, box);
     if (rc) return rc;
   }
@@ -1712,6 +1753,8 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   p.stages = pl.stages;
   p.ni = pl.ni;
   p.ws = pl.ws;
+  p.kr = pl.kr;
+  p.hb = pl.hb;
   p.stage_bytes = (int)pl.stage_bytes;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
@@ -1763,7 +1806,7 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   {  // d_ifgo [T,B,4H] as {k, batch row, t}
     uint64_t dims[3] = {(uint64_t)4 * H, (uint64_t)B, (uint64_t)T};
     uint64_t str[2] = {(uint64_t)4 * H * 2, (uint64_t)B * 4 * H * 2};
-    uint32_t box[3] = {RK, RB, 1};
+    uint32_t box[3] = {RK, (uint32_t)(pl.hb / 128), 1};
     rc = encode_tensor_map(&tg, d_ifgo, 3, dims, str, box);
     if (rc) return rc;
   }
@@ -1783,7 +1826,7 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   p.ep_bytes = (int)pl.ep_bytes;
   p.T = T; p.B = B; p.H = H;
   p.nbt = pl.nbt; p.nug = pl.nug; p.nb_par = pl.nb_par; p.ntl = pl.ntl; p.stages = pl.stages; p.ni = pl.ni;
-  p.ws = pl.ws; p.stage_bytes = (int)pl.stage_bytes;
+  p.ws = pl.ws; p.kr = pl.kr; p.hb = pl.hb; p.stage_bytes = (int)pl.stage_bytes;
   p.alias = pl.alias;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
   p.no_arrive = (d.flags & BLSTM_FLAG_TEST_NO_ARRIVE) ? 1 : 0;
