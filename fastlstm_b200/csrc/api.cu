@@ -63,6 +63,16 @@ static int check_desc(const blstm_desc* d) {
 
 static size_t esize(int dtype) { return dtype == BLSTM_F32 ? 4 : 2; }
 
+// The 16-bit kernels move every tensor in 16-byte pieces (vector loads and stores, TMA): all tensor
+// base pointers must be 16-byte aligned there (null pointers, where allowed, pass).
+template <typename... P>
+static bool aligned16(int dtype, P... ptrs) {
+  if (dtype == BLSTM_F32) return true;
+  uintptr_t m = 0;
+  ((m |= reinterpret_cast<uintptr_t>(ptrs)), ...);
+  return (m & 15u) == 0;
+}
+
 static bool ws_ok(const void* ws, size_t have, size_t need) {
   return ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0 && have >= need;
 }
@@ -97,7 +107,7 @@ int blstm_abi_version(void) { return BLSTM_ABI_VERSION; }
 const char* blstm_strerror(int code) {
   switch (code) {
     case BLSTM_OK: return "ok";
-    case BLSTM_E_INVALID_ARG: return "invalid argument (null pointer, non-positive size or unknown dtype)";
+    case BLSTM_E_INVALID_ARG: return "invalid argument (null pointer, non-positive size, unknown dtype, or a 16-bit tensor not 16-byte aligned)";
     case BLSTM_E_UNSUPPORTED: return "shape/dtype combination not supported";
     case BLSTM_E_WORKSPACE: return "workspace missing, not 256-byte aligned, or too small";
     case BLSTM_E_CUDA: return "CUDA call failed (see blstm_last_cuda_error)";
@@ -174,6 +184,7 @@ int blstm_input_projection(const blstm_desc* d, const void* x, const void* Wx, c
   int rc = check_desc(d);
   if (rc) return rc;
   if (!x || !Wx || !ifgo) return BLSTM_E_INVALID_ARG;
+  if (!aligned16(d->dtype, x, Wx, ifgo)) return BLSTM_E_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const int M = d->seq_len * d->batch, N = 4 * d->hidden_size, K = d->input_size;
   if (sm100_gemm_supported(*d)) return sm100_input_projection(*d, x, Wx, bx, bh, ifgo, st);
@@ -185,6 +196,7 @@ int blstm_fwd_recurrence(const blstm_desc* d, void* ifgo, const void* Wh, void* 
   int rc = check_desc(d);
   if (rc) return rc;
   if (!ifgo || !Wh || !out || !cell) return BLSTM_E_INVALID_ARG;
+  if (!aligned16(d->dtype, ifgo, Wh, out, cell)) return BLSTM_E_INVALID_ARG;
   if (!ws_ok(workspace, workspace_bytes, blstm_workspace_bytes(d, BLSTM_PHASE_FWD))) return BLSTM_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   if (sm100_recurrence_supported(*d, BLSTM_PHASE_FWD))
@@ -199,6 +211,7 @@ int blstm_fwd(const blstm_desc* d, const void* x, const void* h0, const void* c0
   if (rc) return rc;
   if (!x || !Wx || !Wh || !out || !cell || !ifgo) return BLSTM_E_INVALID_ARG;
   if ((h0 == nullptr) != (c0 == nullptr)) return BLSTM_E_INVALID_ARG;
+  if (!aligned16(d->dtype, x, h0, c0, Wx, Wh, bx, bh, out, cell, ifgo)) return BLSTM_E_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t slot = (size_t)d->batch * d->hidden_size * esize(d->dtype);
   if (h0) {
@@ -224,6 +237,7 @@ int blstm_bwd_recurrence(const blstm_desc* d, const void* dout, const void* dh_n
   int rc = check_desc(d);
   if (rc) return rc;
   if (!dout || !ifgo || !cell || !Wh || !d_ifgo || !dh0 || !dc0) return BLSTM_E_INVALID_ARG;
+  if (!aligned16(d->dtype, dout, dh_n, dc_n, ifgo, cell, Wh, d_ifgo, dh0, dc0, db)) return BLSTM_E_INVALID_ARG;
   const BwdLayout L = bwd_layout(*d);
   if (!ws_ok(workspace, workspace_bytes, L.rec_bytes)) return BLSTM_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
@@ -239,6 +253,7 @@ int blstm_dgrad_input(const blstm_desc* d, const void* d_ifgo, const void* Wx, v
   int rc = check_desc(d);
   if (rc) return rc;
   if (!d_ifgo || !Wx || !dx) return BLSTM_E_INVALID_ARG;
+  if (!aligned16(d->dtype, d_ifgo, Wx, dx)) return BLSTM_E_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const int M = d->seq_len * d->batch, N = d->input_size, K = 4 * d->hidden_size;
   if (sm100_gemm_supported(*d)) {
@@ -254,6 +269,7 @@ int blstm_wgrad(const blstm_desc* d, const void* d_ifgo, const void* x, const vo
   int rc = check_desc(d);
   if (rc) return rc;
   if (!d_ifgo || !x || !out || !dWx || !dWh) return BLSTM_E_INVALID_ARG;
+  if (!aligned16(d->dtype, d_ifgo, x, out, dWx, dWh)) return BLSTM_E_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const int TB = d->seq_len * d->batch, G = 4 * d->hidden_size, I = d->input_size, H = d->hidden_size;
   if (sm100_gemm_supported(*d)) {
@@ -271,6 +287,7 @@ int blstm_bias_grad(const blstm_desc* d, const void* d_ifgo, float* db, void* wo
   int rc = check_desc(d);
   if (rc) return rc;
   if (!d_ifgo || !db) return BLSTM_E_INVALID_ARG;
+  if (!aligned16(d->dtype, d_ifgo, db)) return BLSTM_E_INVALID_ARG;
   const BwdLayout L = bwd_layout(*d);
   if (!ws_ok(workspace, workspace_bytes, L.rec_bytes)) return BLSTM_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;

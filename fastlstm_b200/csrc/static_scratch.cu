@@ -48,6 +48,10 @@ int blstm_fwd_recurrence_static(const blstm_desc* d, void* ifgo, const void* Wh,
   if (!d || !ifgo || !Wh || !out || !cell) return BLSTM_E_INVALID_ARG;
   const size_t need = blstm_workspace_bytes(d, BLSTM_PHASE_FWD);
   if (need == 0) return BLSTM_E_INVALID_ARG;            // bad descriptor
+  if (d->dtype != BLSTM_F32 &&
+      ((reinterpret_cast<uintptr_t>(ifgo) | reinterpret_cast<uintptr_t>(Wh) | reinterpret_cast<uintptr_t>(out) |
+        reinterpret_cast<uintptr_t>(cell)) & 15u) != 0)
+    return BLSTM_E_INVALID_ARG;                           // 16-bit tensors move in 16-byte pieces
   if (need > kStaticScratchBytes) return BLSTM_E_TOO_LARGE;
   void* ws = nullptr;
   int rc = static_scratch_ptr(&ws);

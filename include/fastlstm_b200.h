@@ -38,7 +38,8 @@ enum { BLSTM_F32 = 0, BLSTM_F16 = 1, BLSTM_BF16 = 2 };
 /* status codes */
 enum {
   BLSTM_OK = 0,
-  BLSTM_E_INVALID_ARG = 1,     /* null pointer, non-positive size, unknown dtype        */
+  BLSTM_E_INVALID_ARG = 1,     /* null pointer, non-positive size, unknown dtype, or a
+                                  16-bit tensor pointer that is not 16-byte aligned     */
   BLSTM_E_UNSUPPORTED = 2,     /* shape/dtype combination no kernel covers               */
   BLSTM_E_WORKSPACE = 3,       /* workspace pointer null/misaligned or too small         */
   BLSTM_E_CUDA = 4,            /* a CUDA runtime/driver call failed (see blstm_last_cuda_error) */

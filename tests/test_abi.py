@@ -47,6 +47,14 @@ def test_host_only_entry_points():
     # argument validation happens before any CUDA call
     assert lib.blstm_fwd(bad, *([None] * 11), 0, None) == 1
     assert lib.blstm_fwd(d, *([None] * 11), 0, None) == 1
+    # 16-bit tensors move in 16-byte pieces: a misaligned base pointer is refused (fake addresses;
+    # the check comes before anything touches them)
+    h = _lib.Desc(_lib.BF16, 8, 128, 64, 64, 0, 0, 0)
+    ok_ptr, odd_ptr = 0x10000, 0x10002
+    assert lib.blstm_fwd_recurrence(h, odd_ptr, ok_ptr, ok_ptr, ok_ptr, None, 0, None) == 1
+    assert lib.blstm_fwd_recurrence(h, ok_ptr, ok_ptr, ok_ptr, odd_ptr, None, 0, None) == 1
+    assert lib.blstm_fwd_recurrence(h, ok_ptr, ok_ptr, ok_ptr, ok_ptr, None, 0, None) == 3
+    assert lib.blstm_fwd_recurrence_static(h, ok_ptr, odd_ptr, ok_ptr, ok_ptr, None) == 1
 
 
 def test_desc_struct_layout_matches_header():
