@@ -21,6 +21,8 @@
 //   next warp     publisher (interleaved tiles only): proxy fence + release per item
 //   last 4 or 8   epilogue: thread = batch row x 8 or 16 hidden units x 4 gates
 #include <stdio.h>
+#include <algorithm>
+#include <atomic>
 #include <stdlib.h>
 
 #include "generic.cuh"
@@ -803,6 +805,11 @@ struct BwdPlan {
   size_t off_flags, n_flags, off_db, ws_bytes;
 };
 
+// CTAs of the backward kernel that can be resident at once.  Clusters of four do not tile every GPC
+// without a remainder: a B200 with 148 SMs holds 33 of them, 132 CTAs (asked of the occupancy
+// calculator once per process, for the kernel's largest shared-memory footprint; defined behind the kernel).
+static int bwd_cta_capacity();
+
 static BwdPlan make_bwd_plan(const blstm_desc& d) {
   BwdPlan p{};
   p.ok = false;
@@ -813,7 +820,7 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.nbt = cdiv(B, RB);
   p.nug = H / 64;
   const int per_tile = p.nug * 4;
-  const int sms = plan_sm_count();
+  const int sms = std::min(plan_sm_count(), bwd_cta_capacity());
   if (per_tile > sms) return p;
   p.nb_par = sms / per_tile;
   if (p.nb_par > p.nbt) p.nb_par = p.nbt;
@@ -1637,6 +1644,36 @@ __global__ void __launch_bounds__(128) colsum_kernel(const T16* __restrict__ g, 
   float* dst = part + (size_t)blockIdx.y * cols + col;
   *reinterpret_cast<float4*>(dst) = make_float4(s[0], s[1], s[2], s[3]);
   *reinterpret_cast<float4*>(dst + 4) = make_float4(s[4], s[5], s[6], s[7]);
+}
+
+static int bwd_cta_capacity() {
+  static std::atomic<int> cached{0};
+  int c = cached.load(std::memory_order_relaxed);
+  if (c > 0) return c;
+  int cap = 132;
+  DeviceInfo di;
+  if (get_device_info(&di) == BLSTM_OK && di.sm_count > 0) {
+    cap = di.sm_count * 132 / 148 / 4 * 4;
+    auto kern = bwd_kernel<1, __half>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(di.sm_count / 4 * 4);
+      cfg.blockDim = dim3(384);
+      cfg.dynamicSmemBytes = 232448;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 4;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int mc = 0;
+      if (cudaOccupancyMaxActiveClusters(&mc, kern, &cfg) == cudaSuccess && mc > 0) cap = mc * 4;
+    }
+    (void)cudaGetLastError();
+  }
+  cached.store(cap, std::memory_order_relaxed);
+  return cap;
 }
 
 template <int TI, typename T16>

@@ -12,7 +12,8 @@ TD = {"fp16": torch.float16, "bf16": torch.bfloat16}
 # interleaved tiles (UH=32, TI=2); ragged with interleave; ...; narrow slices with two tiles, with four
 # tiles of which one is missing, and with two chunks of interleaved tiles (4 + 1)
 FWD_SHAPES = [(3, 128, 64), (5, 200, 128), (8, 256, 256), (4, 64, 1024), (6, 1300, 512), (4, 2304, 256),
-              (40, 96, 256), (3, 32, 2048), (5, 130, 1536), (4, 384, 1024), (5, 640, 1024), (3, 1280, 1024), (5, 130, 768)]
+              (40, 96, 256), (3, 32, 2048), (5, 130, 1536), (4, 384, 1024), (5, 640, 1024), (3, 1280, 1024), (5, 130, 768),
+              (5, 1024, 512), (3, 4800, 64)]
 
 
 def _desc(dtype, T, B, H, flags=0):
@@ -94,7 +95,8 @@ def test_forward_recurrence(dtype, shape):
 
 
 BWD_SHAPES = [(3, 128, 64), (5, 200, 128), (8, 256, 256), (4, 64, 1024), (6, 1300, 512), (1, 40, 64), (30, 96, 256),
-              (3, 32, 2048), (4, 130, 1536), (4, 384, 1024), (5, 640, 1024), (3, 1280, 1024), (5, 130, 768)]
+              (3, 32, 2048), (4, 130, 1536), (4, 384, 1024), (5, 640, 1024), (3, 1280, 1024), (5, 130, 768),
+              (4, 2304, 256), (5, 1024, 512), (4, 640, 512), (3, 4800, 64), (3, 400, 768), (3, 2000, 320)]
 
 
 def _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh):
