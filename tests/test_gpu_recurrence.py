@@ -279,3 +279,36 @@ def test_cluster_hand_off_forward_matches_general_kernel(dtype, shape):
     _cmp("ifgo vs general kernel", ifgo, ifgo2, tol * 4)
     ifgo3, out3, _ = _fwd(lib, _desc(dtype, T, B, H), pre, Wh, h0, c0)
     assert torch.equal(out, out3) and torch.equal(ifgo, ifgo3)
+
+
+# Geometry sweep: every hidden size class against batches of one row, a ragged second tile, more tiles
+# than CTA rows, and far more (two steps are enough to cross a hand-off in each direction).
+SWEEP_SHAPES = [(2, B, H) for H in (64, 192, 320, 640, 1280, 2048) for B in (1, 129, 1300, 4800)]
+
+
+@pytest.mark.parametrize("shape", SWEEP_SHAPES)
+def test_both_recurrences_over_a_sweep_of_geometries(shape):
+    lib = _lib.load()
+    T, B, H = shape
+    dtype, dt = "bf16", torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(B * 7 + H)
+    pre = torch.randn(T, B, 4 * H, generator=g, device="cuda").to(dt)
+    Wh = ((torch.rand(4 * H, H, generator=g, device="cuda") * 2 - 1) / H ** 0.5).to(dt)
+    h0 = (torch.randn(B, H, generator=g, device="cuda") * 0.3).to(dt)
+    c0 = (torch.randn(B, H, generator=g, device="cuda") * 0.3).to(dt)
+    d = _desc(dtype, T, B, H)
+    assert lib.blstm_plan_name(d, 0) == b"sm100" and lib.blstm_plan_name(d, 1) == b"sm100"
+    ifgo, out, cell = _fwd(lib, d, pre, Wh, h0, c0)
+    rg, ro, rc = _torch_fwd(pre, Wh, h0, c0)
+    _cmp("ifgo", ifgo, rg, 0.12)
+    _cmp("out", out[1:], ro, 3e-2)
+    _cmp("cell", cell[1:], rc, 6e-2)
+    dout = torch.randn(T, B, H, generator=g, device="cuda").to(dt)
+    dh_n = torch.randn(B, H, generator=g, device="cuda").to(dt)
+    dc_n = torch.randn(B, H, generator=g, device="cuda").to(dt)
+    got = _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh)
+    wg, wh, wc = _torch_bwd(dout, dh_n, dc_n, ifgo, cell, Wh)
+    _cmp("d_ifgo", got[0], wg, 4e-2 * max(float(wg.float().abs().max()), 1.0))
+    _cmp("dh0", got[1][None], wh[None], 4e-2 * max(float(wh.abs().max()), 1.0))
+    _cmp("dc0", got[2][None], wc[None], 4e-2 * max(float(wc.abs().max()), 1.0))
+    assert torch.allclose(got[3], got[0].float().sum(dim=(0, 1)), rtol=1e-4, atol=1e-3 * T * B ** 0.5)

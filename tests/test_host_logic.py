@@ -105,3 +105,26 @@ def test_packed_sequence_plumbing_matches_nn_lstm(monkeypatch, bidirectional):
         torch.testing.assert_close(a, b, rtol=1e-9, atol=1e-10)
     for a, b in zip(p1, p2):
         torch.testing.assert_close(a, b, rtol=1e-9, atol=1e-10)
+
+
+def test_persistent_plans_fit_the_device_for_a_sweep_of_shapes():
+    """Every tensor-core plan must be launchable on a 148-SM part: the forward grid within the SM count,
+    the backward grid within the 33 clusters of four that can be resident at once, shared memory
+    within the 227 KB a CTA may have.  (Geometry only: nothing is launched.)"""
+    import re
+    from fastlstm_b200 import plan_detail
+    seen = set()
+    for H in (64, 128, 192, 256, 320, 384, 512, 640, 768, 1024, 1280, 1536, 2048):
+        for B in (1, 32, 100, 128, 129, 256, 400, 512, 640, 1024, 1300, 2048, 2304, 4096, 4800, 8192):
+            for phase in ("fwd", "bwd"):
+                s = plan_detail(torch.bfloat16, 8, B, H, H, phase)
+                assert s.startswith("sm100"), (B, H, phase, s)
+                grid = int(re.search(r"grid=(\d+)", s).group(1))
+                assert grid <= (132 if phase == "bwd" else 148), (B, H, phase, s)
+                if phase == "bwd":
+                    assert grid % 4 == 0, s
+                m = re.search(r"smem=(\d+)", s)
+                if m:
+                    assert int(m.group(1)) <= 232448, (B, H, phase, s)
+                seen.add(re.sub(r"grid=\d+|smem=\d+", "", s))
+    assert len(seen) > 20      # the sweep meets many different plans
