@@ -8,8 +8,10 @@ from fastlstm_b200 import _lib
 pytestmark = pytest.mark.gpu
 
 TD = {"fp16": torch.float16, "bf16": torch.bfloat16}
-# (T, B, I, H): aligned, ragged M, ragged N/K, split-K
-SHAPES = [(4, 64, 64, 64), (3, 50, 72, 40), (16, 128, 256, 256), (64, 256, 512, 128), (7, 33, 136, 200)]
+# (T, B, I, H): aligned, ragged M, ragged N/K, split-K; CTA pairs (N % 256 == 0, M >= 256) with a ragged
+# last tile row, with an odd CTA whose rows are all past M, and over many tiles
+SHAPES = [(4, 64, 64, 64), (3, 50, 72, 40), (16, 128, 256, 256), (64, 256, 512, 128), (7, 33, 136, 200),
+          (5, 77, 256, 64), (3, 100, 128, 128), (40, 512, 512, 512)]
 
 
 def _desc(dtype, T, B, I, H, flags=0):
