@@ -67,7 +67,7 @@ static bool pick_ring(size_t fixed_bytes, size_t stage_bytes, int max_ni, int kc
 
 struct RecPlan {
   bool ok;
-  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages, ni, ws;
+  int UH, N, nh, nbt, nb_par, ntl, TI, grid, epi_warps, threads, stages, ni, nl, ws;
   int npb;                  // interleaved tiles: TMA landing buffers per epilogue warp (1 or 2), else 0
   int kr;                   // K chunks of the Wh slice that stay resident (all of them unless ws)
   int hb;                   // bytes of the h rows in a ring stage: 128 rows, or a single smaller tile's own rows
@@ -147,6 +147,14 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
     fixed += p.ep_bytes;
   }
   if (!pick_ring(fixed, p.stage_bytes, n_issuers, H / RK, &p.stages, &p.ni)) return p;
+  // TMA-issuing lanes of the producer warp (they split the ring's stages; nl | stages).  As many as
+  // issuers by default; measured exceptions (3-4 % each): two interleaved tiles do better with more lanes
+  // (B=2048: 2.55 -> 2.46 ms, B=1024: 1.89 -> 1.78 ms), a single tile on a six-stage ring with fewer
+  // (H=1024: 3.89 -> 3.75 ms).
+  p.nl = p.ni;
+  if (p.TI == 2) p.nl = UH == 32 ? 2 : 4;
+  if (p.TI == 1 && p.stages == 6) p.nl = 2;
+  if (p.stages % p.nl != 0 || p.nl > H / RK) p.nl = p.ni;
   p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)(d.seq_len + 1) * p.nbt;
   p.off_flags = sizeof(Control);
@@ -159,7 +167,8 @@ struct FwdParams {
   int T, B, H;
   int nbt, nh, nb_par, ntl;
   int stages;
-  int ni;                   // TMA-issuing lanes = MMA-issuing warps in use
+  int ni;                   // MMA-issuing warps in use
+  int nl;                   // TMA-issuing lanes of the producer warp (nl divides the ring depth)
   int ws;                   // 1: part of the Wh slice streamed through the ring instead of resident
   int kr;                   // resident K chunks of the Wh slice
   int hb;                   // bytes of the h rows in a ring stage
@@ -322,8 +331,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           bool lane_ok = true;
           // One tile in flight: the wait for each issuing lane's first ring stage (half a thousand clocks
           // even when the stage is long free) is taken BEFORE the counter, off the step's chain.
-          const int kc_first = (lane + nacc - gs % nacc) % nacc;
-          if (TI == 1 && lane < nacc && kc_first < KC) {
+          const int nl = p.nl;                 // TMA-issuing lanes: lane l owns the ring stages == l (mod nl)
+          const int kc_first = (lane + nl - gs % nl) % nl;
+          if (TI == 1 && lane < nl && kc_first < KC) {
             int s = gs + kc_first;
             uint32_t ph = gph;
             while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
@@ -343,9 +353,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
             if (!WRITER_FENCE && !PUBLISHER) fence_proxy_async();
           }
           const int row0 = bt * RB;
-          if (lane < nacc && lane_ok) {
-            // this lane owns ring stages == lane (mod nacc): the item's chunks that land there
-            for (int kc = kc_first; kc < KC; kc += nacc) {
+          if (lane < nl && lane_ok) {
+            // this lane owns ring stages == lane (mod nl): the item's chunks that land there
+            for (int kc = kc_first; kc < KC; kc += nl) {
               int s = gs + kc;
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
@@ -798,7 +808,7 @@ constexpr int XSLOT_BYTES = RB * XROW_BYTES;  // one exchanged slice: 128 rows x
 
 struct BwdPlan {
   bool ok;
-  int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni, ws, alias;
+  int nug, nbt, nb_par, ntl, TI, grid, threads, stages, ni, nl, ws, alias;
   int kr;                   // K chunks of the Wh slice that stay resident (all of them unless ws)
   int hb;                   // bytes of the d_ifgo rows in a ring stage (128 rows, or a single smaller tile's own)
   size_t w_bytes, recv_bytes, stage_bytes, smem, ep_bytes;
@@ -876,6 +886,12 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
       p.alias = 1; p.stages = st2; p.ni = ni2; fixed = fixed2;
     }
   }
+  // TMA-issuing lanes of the producer warp (nl | stages): four interleaved tiles do better with four
+  // (B=4096, H=512: 8.5 -> 8.1 ms), a single tile on a six-stage ring with two (H=1024: 5.33 -> 5.22 ms)
+  p.nl = p.ni;
+  if (p.TI == 4) p.nl = 4;
+  if (p.TI == 1 && p.stages == 6) p.nl = 2;
+  if (p.stages % p.nl != 0 || p.nl > H / RK) p.nl = p.ni;
   p.smem = fixed + (size_t)p.stages * p.stage_bytes;
   p.n_flags = (size_t)d.seq_len * p.nbt;
   p.off_flags = sizeof(Control);
@@ -890,6 +906,7 @@ struct BwdParams {
   int nbt, nug, nb_par, ntl;
   int stages;
   int ni;
+  int nl;                   // TMA-issuing lanes of the producer warp (nl divides the ring depth)
   int ws;
   int kr;                   // resident K chunks of the Wh slice
   int hb;                   // bytes of the d_ifgo rows in a ring stage
@@ -1055,9 +1072,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           if (!WRITER_FENCE && !PUBLISHER) fence_proxy_async();
           const int row0 = bt * RB, col0 = (int)r * H;
           bool lane_ok = true;
-          if (lane < nacc) {
-            // this lane owns ring stages == lane (mod nacc): the item's chunks that land there
-            for (int kc = (lane + nacc - gs % nacc) % nacc; kc < KC; kc += nacc) {
+          const int nl = p.nl;                 // TMA-issuing lanes: lane l owns the ring stages == l (mod nl)
+          if (lane < nl) {
+            // this lane owns ring stages == lane (mod nl): the item's chunks that land there
+            for (int kc = (lane + nl - gs % nl) % nl; kc < KC; kc += nl) {
               int s = gs + kc;
               uint32_t ph = gph;
               while (s >= R_STAGES) { s -= R_STAGES; ph ^= 1; }
@@ -1735,8 +1753,8 @@ int sm100_plan_detail(const blstm_desc& d, int phase, char* buf, size_t n) {
     if (p.ws) snprintf(wh, sizeof(wh), "%d/%d chunks resident, rest streamed", p.kr, d.hidden_size / RK);
     else snprintf(wh, sizeof(wh), "resident");
     return snprintf(buf, n, "sm100 bwd cluster=4 units_per_cluster=64 TI=%d grid=%d threads=%d stages=%d issuers=%d "
-                    "rows_per_stage=%d wh=%s alias=%d smem=%zu", p.TI, p.grid, p.threads, p.stages, p.ni, p.hb / 128, wh,
-                    p.alias, p.smem);
+                    "loaders=%d rows_per_stage=%d wh=%s alias=%d smem=%zu", p.TI, p.grid, p.threads, p.stages, p.ni, p.nl,
+                    p.hb / 128, wh, p.alias, p.smem);
   }
   const RecPlan p = make_plan(d, phase);
   if (!p.ok) return 0;
@@ -1746,8 +1764,8 @@ int sm100_plan_detail(const blstm_desc& d, int phase, char* buf, size_t n) {
   char wh[48];
   if (p.ws) snprintf(wh, sizeof(wh), "%d/%d chunks resident, rest streamed", p.kr, d.hidden_size / RK);
   else snprintf(wh, sizeof(wh), "resident");
-  return snprintf(buf, n, "sm100 fwd UH=%d TI=%d grid=%d threads=%d stages=%d issuers=%d rows_per_stage=%d wh=%s smem=%zu",
-                  p.UH, p.TI, p.grid, p.threads, p.stages, p.ni, p.hb / 128, wh, p.smem);
+  return snprintf(buf, n, "sm100 fwd UH=%d TI=%d grid=%d threads=%d stages=%d issuers=%d loaders=%d rows_per_stage=%d wh=%s smem=%zu",
+                  p.UH, p.TI, p.grid, p.threads, p.stages, p.ni, p.nl, p.hb / 128, wh, p.smem);
 }
 
 int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* out, void* cell, void* ws,
@@ -1800,6 +1818,7 @@ int sm100_fwd_recurrence(const blstm_desc& d, void* ifgo, const void* Wh, void* 
   p.nbt = pl.nbt; p.nh = pl.nh; p.nb_par = pl.nb_par; p.ntl = pl.ntl;
   p.stages = pl.stages;
   p.ni = pl.ni;
+  p.nl = pl.nl;
   p.ws = pl.ws;
   p.kr = pl.kr;
   p.hb = pl.hb;
@@ -1874,6 +1893,7 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   p.ep_bytes = (int)pl.ep_bytes;
   p.T = T; p.B = B; p.H = H;
   p.nbt = pl.nbt; p.nug = pl.nug; p.nb_par = pl.nb_par; p.ntl = pl.ntl; p.stages = pl.stages; p.ni = pl.ni;
+  p.nl = pl.nl;
   p.ws = pl.ws; p.kr = pl.kr; p.hb = pl.hb; p.stage_bytes = (int)pl.stage_bytes;
   p.alias = pl.alias;
   p.fmt = d.dtype == BLSTM_BF16 ? 1 : 0;
