@@ -583,16 +583,36 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           // publish h[t+1] first (it is all the peers wait for): the publisher warp fences and releases
           __syncwarp();
           if (lane == 0) mbar_arrive(&pub_bar[(it - 1) & 3]);
-          // then hand the box to TMA and, once it has been read out of shared memory, fetch the box of
-          // the item `npb` ahead into the landing buffer that just became free
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            const int row0 = bt * RB + q * 32;
-            if (!p.inference) tma_store_4d(&tmP, pbb, unit0, row0, 0, t);
-            tma_store_commit();
-            tma_store_wait_read<0>();
-            issue_load();
+          // then the final pre-activations leave the landing buffer, and the box of the item `npb` ahead is
+          // fetched into it
+          if constexpr (NU == 16) {
+            // Plain stores, NOT a TMA store: an SM's TMA unit writes only ~29 B/clk and the stores queue in
+            // front of the h loads (measured: 8 such boxes per item cut a concurrent h stream from 71 to
+            // 33 B/clk).  Two lanes cover a row's 32 bytes, so a warp instruction writes 16 full sectors:
+            // instruction k = (gate k/2, rows 16*(k%2) ...), lane = (row, 16-byte piece).
+            if (!p.inference) {
+              T16* gbase = reinterpret_cast<T16*>(p.ifgo) + ((size_t)t * p.B + (size_t)bt * RB + q * 32) * (4 * (size_t)H) + unit0;
+              const int r_lo = lane >> 1, v = lane & 1;
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const int g = k >> 1, r = (k & 1) * 16 + r_lo;
+                const uint4 w = *reinterpret_cast<const uint4*>(pbb + g * (64 * NU) + r * 32 + ((v ^ ((r >> 2) & 1)) * 16));
+                if (bt * RB + q * 32 + r < p.B) stg16(gbase + (size_t)r * (4 * (size_t)H) + (size_t)g * H + v * 8, w);
+              }
+            }
+            fence_proxy_async_smem();      // the buffer's reads come before the next box is written into it
+            __syncwarp();
+            if (lane == 0) issue_load();
+          } else {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int row0 = bt * RB + q * 32;
+              if (!p.inference) tma_store_4d(&tmP, pbb, unit0, row0, 0, t);
+              tma_store_commit();
+              tma_store_wait_read<0>();
+              issue_load();
+            }
           }
           __syncwarp();
         }
