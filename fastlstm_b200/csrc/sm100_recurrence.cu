@@ -875,10 +875,10 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   // Cluster exchange: receive slots (3 peers x 8 KB) and send staging (3 x 8 KB), one set.  With
   // interleaved tiles a CTA tells its three peers when it has consumed an item's slices, and nobody
   // stages or ships the next item before all three have said so (`consumed` in the kernel).
-  // Interleaved tiles also move the epilogue's gate traffic through TMA: three landing buffers per
-  // epilogue warp (32 rows x 4 gates x 8 units; d_ifgo is written back in place and stored from there).
+  // Interleaved tiles also move the epilogue's gate traffic through TMA: three landing buffers per pair
+  // of epilogue warps (32 rows x 4 gates x 16 units; d_ifgo is written back in place and stored from there).
   p.recv_bytes = (size_t)2 * 3 * XSLOT_BYTES;
-  p.ep_bytes = p.TI >= 2 ? (size_t)8 * 3 * 2048 : 0;
+  p.ep_bytes = p.TI >= 2 ? (size_t)4 * 3 * 4096 : 0;
   p.kr = resident_chunks(1024 + p.recv_bytes + p.ep_bytes + 1024);
   if (1024 + (size_t)p.kr * 8192 + p.recv_bytes + p.ep_bytes + 1024 + 3 * p.stage_bytes > 232448 && p.TI >= 2) {
     p.TI = 1;                                               // not enough room to interleave tiles
@@ -997,7 +997,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint8_t* recv = smem + (size_t)p.kr * 8192;                 // [3 senders][128 rows][64 B]
   constexpr int XB = 1;                                       // one set of exchange buffers
   uint8_t* stage = recv + (size_t)XB * 3 * XSLOT_BYTES;      // [3 receivers][128 rows][64 B]
-  uint8_t* ep_s = stage + (size_t)XB * 3 * XSLOT_BYTES;      // epilogue TMA buffers [8 warps][3][2 KB]
+  uint8_t* ep_s = stage + (size_t)XB * 3 * XSLOT_BYTES;      // epilogue TMA buffers [4 warp pairs][3][4 KB]
   uint8_t* a_s = p.alias ? recv : ep_s + p.ep_bytes;         // ring (over the exchange buffers if aliased)
   uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + (size_t)R_STAGES * SB);
   uint64_t* full = bars;
@@ -1013,8 +1013,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   uint64_t* pub_bar = reinterpret_cast<uint64_t*>(pub_cnt + 4);   // [4] item published? by item index mod 4
   uint64_t* rdy = pub_bar + 4;                                 // aliased buffers: the 3 peers are done with their MMAs
   uint64_t* consumed = rdy + 1;                                // interleaved tiles: the 3 peers' 8 warps read an item's slices
-  uint64_t* pre_full = consumed + 1;                           // [8 epilogue warps][3] landing buffer filled
-  uint64_t* pre_free = pre_full + 24;                          // [8 epilogue warps][3] landing buffer may be refilled
+  uint64_t* pre_full = consumed + 1;                           // [4 warp pairs][3] landing buffer filled
+  uint64_t* pre_done = pre_full + 12;                          // [4 warp pairs][3] both warps wrote their d_ifgo halves
+  uint64_t* pre_free = pre_full + 24;                          // [4 warp pairs][3] landing buffer may be refilled
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t r = cluster_ctarank();                       // gate whose K range this CTA owns
@@ -1032,10 +1033,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     for (int j = 0; j < 2; ++j) { mbar_init(&xchg[j], 1); mbar_init(&staged[j], ITEM_WARPS); }   // xchg: one expect_tx arrival + tx bytes
     *dead = 0;
     for (int i = 0; i < 4; ++i) pub_cnt[i] = 0;
-    for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], ITEM_WARPS);
+    for (int i = 0; i < 4; ++i) mbar_init(&pub_bar[i], TMAEP ? 4 : ITEM_WARPS);   // (interleaved: one arrival per warp pair)
     mbar_init(rdy, 3);
     mbar_init(consumed, 3 * ITEM_WARPS);
-    for (int i = 0; i < 24; ++i) { mbar_init(&pre_full[i], 1); mbar_init(&pre_free[i], 1); }
+    for (int i = 0; i < 24; ++i) { mbar_init(&pre_full[i], i < 12 ? 1 : 2); mbar_init(&pre_free[i], 1); }
     fence_mbar_init();
     for (int s = 0; s < R_STAGES; ++s) mbar_expect_tx(&full[s], (p.ws && s % KC >= p.kr) ? SB : HB);
     tma_prefetch_desc(&tmW);
@@ -1139,17 +1140,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           }
         }
       }
-    } else if (TMAEP && lane <= ITEM_WARPS) {
-      // ------------------------------------------------------------ gate loaders (lanes 1..8)
-      // Lane 1+w fetches epilogue warp w's gate boxes, up to three gate-maths items ahead, into the
-      // warp's three landing buffers in turn; a buffer is refilled once the warp has said that the
-      // d_ifgo box it held has been written (pre_free).  Issuing these loads from here rather than
-      // from the epilogue warps matters: a TMA issue waits for room behind the producer's 16 KB
-      // boxes (about a thousand clocks), which the epilogue warps cannot afford.
+    } else if (TMAEP && lane <= 4) {
+      // ------------------------------------------------------------ gate loaders (lanes 1..4)
+      // Lane 1+w fetches the gate boxes of the two epilogue warps of row quarter w (all 16 units: 32-byte
+      // rows), up to three gate-maths items ahead, into the pair's three landing buffers in turn; a
+      // buffer is refilled once the pair has said that the d_ifgo box it held has been written
+      // (pre_free).  Issuing these loads from here rather than from the epilogue warps matters: a TMA
+      // issue waits for room behind the producer's 16 KB boxes (about a thousand clocks), which the
+      // epilogue warps cannot afford.
       const int w = lane - 1;
-      const int gq = (FIRST_EPI + w) & 3, gu = w >> 2;          // the warp's row quarter and unit half
-      const int g_unit0 = ugc * 64 + (int)r * 16 + gu * 8;
-      uint8_t* g_buf = ep_s + (size_t)w * 3 * 2048;
+      const int gq = w;                                         // the pair's row quarter
+      const int g_unit0 = ugc * 64 + (int)r * 16;
+      uint8_t* g_buf = ep_s + (size_t)w * 3 * 4096;
       ItemCursor<TI> lc;
       lc.init();
       int n = 0;
@@ -1158,8 +1160,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
         const int b = n % 3;
         wc.d0 = T - 1 - lc.t; wc.d1 = lc.tile(pb, p.nb_par);
         if (n >= 3 && !mbar_wait(&pre_free[3 * w + b], (uint32_t)(n / 3 - 1) & 1u, wc)) { ok = false; break; }
-        mbar_expect_tx(&pre_full[3 * w + b], 2048);
-        tma_load_4d(g_buf + b * 2048, &tmI, &pre_full[3 * w + b], g_unit0, lc.tile(pb, p.nb_par) * RB + gq * 32, 0,
+        mbar_expect_tx(&pre_full[3 * w + b], 4096);
+        tma_load_4d(g_buf + b * 4096, &tmI, &pre_full[3 * w + b], g_unit0, lc.tile(pb, p.nb_par) * RB + gq * 32, 0,
                     T - 1 - lc.t);
         ++n;
       }
@@ -1249,18 +1251,19 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
     int it = 0;                 // MMA items consumed so far: TMEM buffer it & 1, on its (it >> 1)-th use
     int pub_it = 0;             // gate-maths items published so far
     bool ok = true;
-    // Interleaved tiles: this warp's three landing buffers [4 gates][32 rows][8 units] (16-byte rows
-    // back to back: the 32 lanes' pieces of one gate fall into different banks), used in turn by
-    // consecutive gate-maths items; a lane of the publisher warp issues the warp's TMA loads, lane 0 of
-    // the warp its stores.  An item's store is only waited for one item later (by then it has long
-    // completed): that is when its buffer is handed back to the loader and when the warp counts the
-    // item in.
-    const int ew = warp - FIRST_EPI;
-    uint8_t* pbuf = ep_s + (size_t)ew * 3 * 2048;
-    uint64_t* pfull = pre_full + 3 * ew;
-    bool pending = false;             // lane 0: the previous item's store has not been waited for yet
-    auto p_off = [&](int k) { return k * 512 + lane * 16; };
-    uint64_t* pfree = pre_free + 3 * ew;
+    // Interleaved tiles: the two warps of a row quarter (one per unit half) share three landing buffers
+    // [4 gates][32 rows][16 units] (32-byte rows with the 32-byte swizzle: a warp's 16-byte pieces of one
+    // gate fall into different banks), used in turn by consecutive gate-maths items.  Whole 32-byte
+    // segments matter: an SM's TMA unit is what bounds an item, and its cost goes by row segments - eight
+    // boxes of 16-byte segments in and eight out per item cost it about twice the item's 128 KB of d_ifgo
+    // chunks.  A lane of the publisher warp issues the pair's TMA loads; lane 0 of the pair's first warp
+    // issues its store once both warps have written their halves (pre_done); when the store has completed
+    // the buffer is handed back to the loader and the pair counts the item in.
+    uint8_t* pbuf = ep_s + (size_t)q * 3 * 4096;
+    uint64_t* pfull = pre_full + 3 * q;
+    uint64_t* pdone = pre_done + 3 * q;
+    auto p_off = [&](int k) { return k * 1024 + lane * 32 + ((g ^ ((lane >> 2) & 1)) * 16); };
+    uint64_t* pfree = pre_free + 3 * q;
     for (int ch = 0; ch < n_chunks && ok; ++ch) {
       // dc is carried per interleaved tile; dh is rebuilt from the accumulator in every item, so one
       // copy serves all tiles (its first value, the gradient of h_n, is fetched in the tile's first item)
@@ -1345,7 +1348,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
       auto fetch_gates = [&]() -> bool {
         if constexpr (TMAEP) {
           if (!mbar_wait(&pfull[pub_it % 3], (uint32_t)(pub_it / 3) & 1u, wc)) return false;
-          const uint8_t* pbb = pbuf + (pub_it % 3) * 2048;
+          const uint8_t* pbb = pbuf + (pub_it % 3) * 4096;
 #pragma unroll
           for (int k = 0; k < 4; ++k) pf[k] = *reinterpret_cast<const uint4*>(pbb + p_off(k));
         }
@@ -1535,26 +1538,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
               // d_ifgo[t] goes back into the landing buffer the gates came from and leaves as one box.
               // The PREVIOUS item's box has been written by now: its buffer takes the gates of the item
               // two ahead, and (the peers' producers read d_ifgo next) the warp counts that item in.
-              uint8_t* pbb = pbuf + (pub_it % 3) * 2048;
+              uint8_t* pbb = pbuf + (pub_it % 3) * 4096;
               *reinterpret_cast<uint4*>(pbb + p_off(0)) = make_uint4(qi[0], qi[1], qi[2], qi[3]);
               *reinterpret_cast<uint4*>(pbb + p_off(1)) = make_uint4(qf[0], qf[1], qf[2], qf[3]);
               *reinterpret_cast<uint4*>(pbb + p_off(2)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
               *reinterpret_cast<uint4*>(pbb + p_off(3)) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
               fence_proxy_async_smem();
               __syncwarp();
-              if (lane == 0) {
-                tma_store_4d(&tmD, pbb, unit0, bt * RB + q * 32, 0, t);
+              if (lane == 0) mbar_arrive(&pdone[pub_it % 3]);      // this warp's half of the box is in place
+              if (lane == 0 && g == 0 && mbar_wait(&pdone[pub_it % 3], (uint32_t)(pub_it / 3) & 1u, wc)) {
+                tma_store_4d(&tmD, pbb, unit0, bt * RB + q * 32, 0, t);      // (g == 0: unit0 is the pair's first unit)
                 tma_store_commit();
-                // The wait may only be put off while the next item does not need THIS one: not when this
-                // CTA walks a single tile in this chunk (the tile's next step is the next item), nor in
-                // the chunk's last step (the closing items store nothing, so nobody would publish it).
-                // Nor with two interleaved tiles: they are bound by the hand-off chain, and a deferred
-                // count-in would chain each tile's publication to the other tile's next item.
-                const bool now = TI == 2 || (pb + (ch * TI + 1) * p.nb_par >= p.nbt) || st == T - 1;
-                if (now) tma_store_wait<0>(); else tma_store_wait<1>();   // <1>: all but the store just issued
-                if (pending) { mbar_arrive(&pfree[(pub_it - 1) % 3]); mbar_arrive(&pub_bar[(pub_it - 1) & 3]); }
-                if (now) { mbar_arrive(&pfree[pub_it % 3]); mbar_arrive(&pub_bar[pub_it & 3]); }
-                pending = !now;
+                // The peers' producers read d_ifgo[t] next, so the pair counts the item in only once the
+                // store has completed, and it waits for that at once: putting the wait off by an item (when
+                // it costs nothing) lengthens every tile's hand-off chain by that item, and the chain is
+                // what bounds the step even with four tiles interleaved (B=4096, H=512: 8.28 -> 7.75 ms).
+                tma_store_wait<0>();
+                mbar_arrive(&pfree[pub_it % 3]);
+                mbar_arrive(&pub_bar[pub_it & 3]);
               }
             } else if (row_ok) {
               T16* dstp = dg + ((size_t)t * p.B + row) * H4 + unit0;
@@ -1618,10 +1619,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
           }
         }
       }
-    }
-    if (TMAEP && lane == 0) {
-      tma_store_wait<0>();
-      if (pending) { mbar_arrive(&pfree[(pub_it - 1) % 3]); mbar_arrive(&pub_bar[(pub_it - 1) & 3]); }
     }
     if (want_db) {
       float* dst = p.db_part + ((size_t)pb * 4 + q) * H4 + unit0;
@@ -1899,13 +1896,14 @@ int sm100_bwd_recurrence(const blstm_desc& d, const void* dout, const void* dh_n
   }
   CUtensorMap ti = tg, td = tg;     // only read by the kernels that interleave tiles
   if (pl.TI >= 2) {
-    // ifgo and d_ifgo [T,B,4H] as {unit, batch row, gate, t}: a box is one warp's 4 gates x 32 rows x 8 units
+    // ifgo and d_ifgo [T,B,4H] as {unit, batch row, gate, t}: a box is a warp pair's 4 gates x 32 rows x 16 units
+    // (32-byte rows, 32-byte swizzle)
     uint64_t dims[4] = {(uint64_t)H, (uint64_t)B, 4, (uint64_t)T};
     uint64_t str[3] = {(uint64_t)4 * H * 2, (uint64_t)H * 2, (uint64_t)B * 4 * H * 2};
-    uint32_t box[4] = {8, 32, 4, 1};
-    rc = encode_tensor_map(&ti, ifgo, 4, dims, str, box, 2, 0);
+    uint32_t box[4] = {16, 32, 4, 1};
+    rc = encode_tensor_map(&ti, ifgo, 4, dims, str, box, 2, 32);
     if (rc) return rc;
-    rc = encode_tensor_map(&td, d_ifgo, 4, dims, str, box, 2, 0);
+    rc = encode_tensor_map(&td, d_ifgo, 4, dims, str, box, 2, 32);
     if (rc) return rc;
   }
   BLSTM_CUDA_OK(cudaMemsetAsync(ws, 0, pl.off_db, st));
