@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory.
 
-Runs ONLY where the reference checkout is available (argument 1, default
-/root/reference).  It imports the reference's pure-PyTorch LSTM path
+Runs ONLY where a checkout of the reference is available: its directory is
+argument 1, or the environment variable FASTLSTM_REFERENCE.  It imports the reference's pure-PyTorch LSTM path
 (fastlstm/lstm.py:1087-1245, `naive_lstm_fwd`, `naive_lstm_bwd`,
 `FastLSTM(version="naive-pt")`) on CPU through two stubs that leave the
 reference untouched: a dummy `flashrnn` module (third-party competitor wrapper
@@ -47,7 +47,10 @@ def u(gen, *shape, k):
 
 
 def main():
-    ref = import_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FASTLSTM_REFERENCE")
+    if not where:
+        sys.exit("usage: make_golden.py <directory of the reference checkout>")
+    ref = import_reference(where)
     torch.set_num_threads(1)
 
     # ---- A: one layer through naive_lstm_fwd / naive_lstm_bwd, non-zero h0,c0,dc_n
