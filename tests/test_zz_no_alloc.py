@@ -68,3 +68,24 @@ def test_static_scratch_entry_rejects_problems_beyond_its_capacity():
                                          torch.cuda.current_stream().cuda_stream)
     assert rc == _lib.E_TOO_LARGE
     assert "capacity" in _lib.strerror(rc)
+
+
+def test_static_scratch_entry_reports_a_wait_that_ran_out_and_recovers():
+    """The bounded waits of the persistent kernel report through the library's own control block too: with
+    the test hook that makes CTAs skip their arrivals every wait runs out after 20 ms (nothing faults,
+    nothing hangs), the status call returns the timeout, and the next call is clean and correct."""
+    lib = _lib.load()
+    dtype, T, B, H = torch.bfloat16, 6, 300, 256
+    pre, Wh, h0, c0 = _inputs(dtype, T, B, H, 21)
+    s = torch.cuda.current_stream().cuda_stream
+    bad = _lib.Desc(_lib.BF16, T, B, H, H, _lib.FLAG_TEST_NO_ARRIVE | _lib.FLAG_NO_CLUSTER, 20000, 0)
+    ifgo = pre.clone()
+    st = torch.zeros(2, T + 1, B, H, device="cuda", dtype=dtype)
+    assert lib.blstm_fwd_recurrence_static(bad, ifgo.data_ptr(), Wh.data_ptr(), st[0].data_ptr(), st[1].data_ptr(), s) == 0
+    assert lib.blstm_static_scratch_status(None, s) == _lib.E_WAIT_TIMEOUT
+    torch.cuda.synchronize()
+    d = _lib.Desc(_lib.BF16, T, B, H, H, 0, 0, 0)
+    want = _run(lib, d, pre, Wh, h0, c0, static=False)
+    got = _run(lib, d, pre, Wh, h0, c0, static=True)
+    for name, a, b in zip(("ifgo", "out", "cell"), got, want):
+        assert torch.equal(a, b), f"{name} differs after a timed-out call"
