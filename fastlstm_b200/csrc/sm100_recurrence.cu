@@ -133,7 +133,7 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.kr = p.ws ? 0 : H / RK;
   // Interleaved tiles: the epilogue's gate traffic goes through TMA.  Every epilogue warp owns
   // landing buffers for its 32 rows' projected pre-activations (4 gates x NU units; the final
-  // pre-activations are written back in place and stored from there).
+  // pre-activations are written back in place and leave from there).
   // Two landing buffers per warp (the next item's box is fetched a whole item ahead) when the ring
   // still gets four stages, else one.
   p.npb = 0;
@@ -216,10 +216,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUte
   constexpr int N = 4 * UH;
   // Interleaved tiles are throughput bound, and there the epilogue's row-strided 16-byte global
   // accesses (a thread owns a batch row: 32 sectors per warp instruction) were the bottleneck: the
-  // projected pre-activations come in, and the final pre-activations go out, as TMA boxes through
-  // shared memory, one set of buffers per epilogue warp (tmP: ifgo as {unit, row, gate, step}): eight
-  // of the twelve 16-byte accesses a thread makes per 8 units.  h keeps its direct stores (they are
-  // what the step hand-off orders) and so do the cell rows (a buffer for them would cost a ring stage).
+  // projected pre-activations come in as TMA boxes through shared memory, one set of buffers per
+  // epilogue warp (tmP: ifgo as {unit, row, gate, step}), and the final pre-activations go out from
+  // the same buffers (16 units per thread: coalesced plain stores; 8 units: a TMA box): eight of the
+  // twelve 16-byte accesses a thread makes per 8 units.  h keeps its direct stores (they are what
+  // the step hand-off orders) and so do the cell rows (a buffer for them would cost a ring stage).
   constexpr bool TMAEP = (TI >= 2);
   // Epilogue warps.  A single tile of 16 units is latency bound and runs best as one warpgroup with
   // 16 units per thread next to four issuers (9 warps); every other shape uses two warpgroups that
