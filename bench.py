@@ -401,7 +401,7 @@ def main():
     value = tokens / (ms_step * 1e-3)
     e2e_value = tokens / (ms_e2e / args.steps * 1e-3)
 
-    # ---- roofline: both persistent recurrence kernels timed alone (rank-local, CUDA events on the
+    # ---- roofline: both persistent recurrence kernels timed by themselves (rank-local, CUDA events on the
     # launching stream); the slower one is the dominant kernel of the step and goes in "roofline"
     hbm_gbs, tflops, which = peaks()
     es = ESIZE[cfg["dtype"]]
@@ -414,9 +414,14 @@ def main():
     nws = lib.blstm_workspace_bytes(d, _lib.PHASE_FWD)
     ws = torch.empty(nws, dtype=torch.uint8, device=dev)
 
-    def time_launch(fn, prep=None, n=5, w=3):
-        durs = []
+    # Each timed launch runs directly behind a full step of the benchmark (no host synchronisation in
+    # between), so it sees the clocks of the timed region: under the power cap of a long step the SMs
+    # run ~10 % slower than for a kernel launched on an idle GPU, and these kernels are latency bound.
+    # The launch gets the arguments the step gives it (the bias gradient included).
+    def time_launch(fn, prep=None, n=5, w=2):
+        pairs = []
         for i in range(w + n):
+            step(x_dev)
             if prep:
                 prep()
             if flush_buf is not None:
@@ -425,10 +430,11 @@ def main():
             e0.record()
             fn()
             e1.record()
-            torch.cuda.synchronize()
             if i >= w:
-                durs.append(e0.elapsed_time(e1))
-        return sum(durs) / len(durs)
+                pairs.append((e0, e1))
+        torch.cuda.synchronize()
+        F.check_status()
+        return sum(a.elapsed_time(b) for a, b in pairs) / len(pairs)
 
     fwd_ms = time_launch(
         lambda: _lib.check(lib.blstm_fwd_recurrence(d, ifgo.data_ptr(), Wh.data_ptr(), states[0].data_ptr(),
@@ -440,11 +446,12 @@ def main():
         wsb = torch.empty(nwb, dtype=torch.uint8, device=dev)
         dg = torch.empty_like(pre)
         carries = torch.empty(2, B, H, device=dev, dtype=dt)
+        db = torch.empty(4 * H, device=dev, dtype=torch.float32)
         kernels["backward recurrence"] = time_launch(
             lambda: _lib.check(lib.blstm_bwd_recurrence(d, dout.data_ptr() if not cfg["batch_first"] else pre.data_ptr(),
                                                         None, None, ifgo.data_ptr(), states[1].data_ptr(), Wh.data_ptr(),
-                                                        dg.data_ptr(), carries[0].data_ptr(), carries[1].data_ptr(), None,
-                                                        wsb.data_ptr(), nwb, st), "bwd_recurrence"))
+                                                        dg.data_ptr(), carries[0].data_ptr(), carries[1].data_ptr(),
+                                                        db.data_ptr(), wsb.data_ptr(), nwb, st), "bwd_recurrence"))
         del dg, wsb
     per_step = 10.0 if cfg["bwd"] else 5.0                    # forward-only runs save nothing for backward
     alg_bytes = per_step * B * H * es * T + 4.0 * H * H * es   # per_step*B*H*e per step + Wh once
