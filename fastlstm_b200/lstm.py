@@ -405,8 +405,10 @@ class FastLSTM(nn.Module):
     same kernels on the time-reversed input and concatenates the two directions' outputs
     (states are ordered layer-major, direction-minor, like nn.LSTM); `dropout` is applied to
     the outputs of every layer but the last while training; a `PackedSequence` input gives a
-    `PackedSequence` output and the states at every sequence's own last step.  `proj_size` is not
-    implemented."""
+    `PackedSequence` output and the states at every sequence's own last step.  `proj_size` > 0 adds
+    nn.LSTM's output projection (`weight_hr_l{k}`: h_t = W_hr (o * tanh(c_t)), recurrent weights
+    [4H, proj_size]); a projected layer runs step by step - one launch of the cell per timestep
+    with the projection between the steps - which is complete but not fast."""
 
     def __init__(self, input_size, hidden_size, num_layers=1, *, bias=True, batch_first=False,
                  version="persistent", device=None, dtype=None, dropout=0.0, bidirectional=False,
@@ -419,14 +421,17 @@ class FastLSTM(nn.Module):
             raise TypeError("bias and batch_first must be bool")
         if version != "persistent":
             raise ValueError(f"Not implemented: {version} (only 'persistent' exists)")
-        if proj_size != 0:
-            raise NotImplementedError("proj_size is not implemented")
+        if not isinstance(proj_size, int) or proj_size < 0:
+            raise ValueError("proj_size should be a positive integer or zero to disable projections")
+        if proj_size >= hidden_size:
+            raise ValueError("proj_size has to be a positive integer, smaller than hidden_size")
         if not 0.0 <= float(dropout) <= 1.0:
             raise ValueError("dropout should be a number in range [0, 1]")
         self.input_size, self.hidden_size, self.num_layers = input_size, hidden_size, num_layers
         self.bias, self.batch_first, self.version = bias, batch_first, version
         self.dropout, self.bidirectional = float(dropout), bool(bidirectional)
         self.num_directions = 2 if bidirectional else 1
+        self.proj_size = proj_size
         self._sinks = None            # per (layer, direction) gradient sinks of a GradBucket, or None
         k = 1.0 / hidden_size ** 0.5
         fk = dict(device=device, dtype=dtype)
@@ -434,14 +439,17 @@ class FastLSTM(nn.Module):
         def u(*shape):
             return nn.Parameter(torch.rand(*shape, **fk) * 2 * k - k)
 
+        out_size = proj_size if proj_size > 0 else hidden_size       # width of h (and of a layer's output)
         for layer in range(num_layers):
-            in_l = input_size if layer == 0 else hidden_size * self.num_directions
+            in_l = input_size if layer == 0 else out_size * self.num_directions
             for sfx in self._suffixes():
                 setattr(self, f"weight_ih_l{layer}{sfx}", u(4 * hidden_size, in_l))
-                setattr(self, f"weight_hh_l{layer}{sfx}", u(4 * hidden_size, hidden_size))
+                setattr(self, f"weight_hh_l{layer}{sfx}", u(4 * hidden_size, out_size))
                 if bias:
                     setattr(self, f"bias_ih_l{layer}{sfx}", u(4 * hidden_size))
                     setattr(self, f"bias_hh_l{layer}{sfx}", u(4 * hidden_size))
+                if proj_size > 0:
+                    setattr(self, f"weight_hr_l{layer}{sfx}", u(proj_size, hidden_size))
 
     def _suffixes(self):
         return ("", "_reverse") if self.bidirectional else ("",)
@@ -450,6 +458,26 @@ class FastLSTM(nn.Module):
         sfx = "_reverse" if reverse else ""
         g = lambda n: getattr(self, f"{n}_l{layer}{sfx}", None)
         return g("weight_ih"), g("bias_ih"), g("weight_hh"), g("bias_hh")
+
+    def _projected_layer(self, x_d, h0, c0, Wx, bx, Wh, bh, Whr, inference):
+        """One direction of one layer with an output projection (nn.LSTM's proj_size): the recurrent
+        input is the projected state, so the layer is run as T single-step calls of the cell (the same
+        operator with T = 1; the projected state is zero-padded to the cell's width and `Wh` [4H,P] to
+        [4H,H], which is exact) with the projection h_t = (o * tanh(c_t)) W_hr^T in between.  Autograd
+        chains the steps.  Returns (out [T,B,P], cells [T,B,H], h_n [B,P], c_n [B,H])."""
+        T, B = x_d.shape[0], x_d.shape[1]
+        H, P = self.hidden_size, self.proj_size
+        pad = torch.nn.functional.pad
+        Wh_wide = pad(Wh, (0, H - P))
+        h = x_d.new_zeros(B, P) if h0 is None else h0
+        c = c0
+        outs, cells = [], []
+        for t in range(T):
+            o, _, c = PersistentLSTMfn.apply(x_d[t:t + 1], pad(h, (0, H - P)), c, Wx, bx, Wh_wide, bh, inference, None)
+            h = o[0] @ Whr.t()
+            outs.append(h)
+            cells.append(c)
+        return torch.stack(outs), torch.stack(cells), h, c
 
     def forward(self, x, h_c_0=None):
         if isinstance(x, torch.nn.utils.rnn.PackedSequence):
@@ -511,7 +539,16 @@ class FastLSTM(nn.Module):
                 hl, cl = h_0[layer * nd + d], c_0[layer * nd + d]
                 inference = _nothing_to_save(x_d, hl, cl, Wx, bx, Wh, bh)
                 sink = None if self._sinks is None else self._sinks[layer * nd + d]
-                if lengths is None:
+                if self.proj_size > 0:
+                    Whr = getattr(self, f"weight_hr_l{layer}{'_reverse' if d == 1 else ''}")
+                    if hl is not None and cl is None or hl is None and cl is not None:
+                        raise ValueError("h_0 and c_0 must both be given or both be None")
+                    cl_ = x_d.new_zeros(B, self.hidden_size) if cl is None else cl
+                    o, cells, h_i, c_i = self._projected_layer(x_d, hl, cl_, Wx, bx, Wh, bh, Whr, inference)
+                    if lengths is not None:
+                        h_i, c_i = at_last(o), at_last(cells)
+                        o = o * valid[:, :, None].to(o.dtype)
+                elif lengths is None:
                     o, h_i, c_i = PersistentLSTMfn.apply(x_d, hl, cl, Wx, bx, Wh, bh, inference, sink)
                 else:
                     o, _, _, cells = PersistentLSTMfn.apply(x_d, hl, cl, Wx, bx, Wh, bh, inference, sink, True)

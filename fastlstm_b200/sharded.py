@@ -66,7 +66,7 @@ class GradBucket:
         self._pending = []          # (segment index, work handle or None)
         self._filled = set()
         from .lstm import FastLSTM
-        if isinstance(module, FastLSTM):
+        if isinstance(module, FastLSTM) and module.proj_size == 0:    # (projected layers: plain-module path)
             self._init_segments(module, dev)
         else:
             n = sum(p.numel() for p in self.params)

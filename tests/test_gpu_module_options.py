@@ -145,3 +145,48 @@ def test_packed_sequence_matches_nn_lstm(dtype, bidirectional, H):
         else:
             e = float(np.linalg.norm(got[k] - want[k]) / max(np.linalg.norm(want[k]), 1e-30))
             assert e <= 5e-2, (k, e)
+
+
+@pytest.mark.parametrize("dtype,bidirectional,H,P", [("fp32", False, 24, 10), ("fp32", True, 40, 16), ("bf16", False, 128, 64)])
+def test_proj_size_matches_nn_lstm(dtype, bidirectional, H, P):
+    """Output projection (nn.LSTM's proj_size; the reference lists it as missing, README.md:92-93):
+    outputs, projected h_n, c_n and every gradient (weight_hr included) against torch.nn.LSTM in float64."""
+    import fastlstm_b200 as F
+    T, B, I, L = 7, 6, 16, 2
+    dt = TORCH_DT[dtype]
+    nd = 2 if bidirectional else 1
+    torch.manual_seed(31)
+    ref = torch.nn.LSTM(I, H, num_layers=L, bidirectional=bidirectional, proj_size=P).double()
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.to(dt).double())
+    m = F.FastLSTM(I, H, num_layers=L, bidirectional=bidirectional, proj_size=P, device="cuda", dtype=dt)
+    assert [n for n, _ in m.named_parameters()] == [n for n, _ in ref.named_parameters()]
+    m.load_state_dict({k: v.to(dt) for k, v in ref.state_dict().items()})
+    g = torch.Generator().manual_seed(32)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(dt).double()
+    x, dout = rnd(T, B, I), rnd(T, B, nd * P)
+    h0, c0 = rnd(L * nd, B, P) * 0.1, rnd(L * nd, B, H) * 0.1
+    h0, c0 = h0.to(dt).double(), c0.to(dt).double()
+
+    def go(mod, cast):
+        xi = cast(x).requires_grad_(True)
+        out, (hn, cn) = mod(xi, (cast(h0), cast(c0)))
+        torch.autograd.backward([out, hn], [cast(dout), torch.ones_like(hn)])
+        f = lambda t: t.detach().double().cpu().numpy()
+        res = {"out": f(out), "h_n": f(hn), "c_n": f(cn), "dx": f(xi.grad)}
+        for n, p in mod.named_parameters():
+            res["grad:" + n] = f(p.grad)
+        return res
+
+    got = go(m, lambda t: t.to("cuda", dt))
+    want = go(ref, lambda t: t.clone())
+    F.check_status()
+    assert got["out"].shape == (T, B, nd * P) and got["h_n"].shape == (L * nd, B, P) and got["c_n"].shape == (L * nd, B, H)
+    for k in want:
+        if dtype == "fp32":
+            assert max_rel(got[k], want[k]) <= 2e-5, k
+        elif k in ("out", "h_n", "c_n"):
+            assert np.abs(got[k] - want[k]).max() <= 2e-2, k
+        else:
+            assert max_rel(got[k], want[k]) <= 5e-2, k

@@ -47,8 +47,8 @@ def test_bidirectional_parameters_match_nn_lstm_and_options_are_validated():
            [(n, tuple(p.shape)) for n, p in ref.named_parameters()]
     m.load_state_dict(ref.state_dict())
     ref.load_state_dict(m.state_dict())
-    with pytest.raises(NotImplementedError):
-        FastLSTM(4, 4, proj_size=2)
+    with pytest.raises(ValueError):
+        FastLSTM(4, 4, proj_size=4)           # like nn.LSTM: smaller than hidden_size
     with pytest.raises(ValueError):
         FastLSTM(4, 4, dropout=1.5)
 
@@ -128,3 +128,47 @@ def test_persistent_plans_fit_the_device_for_a_sweep_of_shapes():
                     assert int(m.group(1)) <= 232448, (B, H, phase, s)
                 seen.add(re.sub(r"grid=\d+|smem=\d+", "", s))
     assert len(seen) > 20      # the sweep meets many different plans
+
+
+@pytest.mark.parametrize("bidirectional", [False, True])
+def test_proj_size_plumbing_matches_nn_lstm(monkeypatch, bidirectional):
+    """nn.LSTM's output projection (proj_size): parameter names, shapes and order, the stepwise layer with
+    the projected state zero-padded to the cell's width, initial states of the projected width, packed
+    input - checked on CPU with a torch stand-in for the CUDA cell against torch.nn.LSTM."""
+    import fastlstm_b200.lstm as mod
+    from torch.nn.utils.rnn import pack_padded_sequence
+    monkeypatch.setattr(mod, "PersistentLSTMfn", _TorchLayer)
+    torch.manual_seed(7)
+    I, H, P, L = 5, 8, 3, 2
+    ref = torch.nn.LSTM(I, H, num_layers=L, bidirectional=bidirectional, proj_size=P).double()
+    m = mod.FastLSTM(I, H, num_layers=L, bidirectional=bidirectional, proj_size=P, dtype=torch.float64)
+    assert [n for n, _ in m.named_parameters()] == [n for n, _ in ref.named_parameters()]
+    assert [tuple(p.shape) for p in m.parameters()] == [tuple(p.shape) for p in ref.parameters()]
+    m.load_state_dict(ref.state_dict())
+    nd = 2 if bidirectional else 1
+    x = torch.randn(6, 4, I, dtype=torch.float64)
+    h0, c0 = torch.randn(L * nd, 4, P, dtype=torch.float64), torch.randn(L * nd, 4, H, dtype=torch.float64)
+    for packed in (False, True):
+        results = []
+        for net in (ref, m):
+            xi = x.clone().requires_grad_()
+            inp = pack_padded_sequence(xi, torch.tensor([6, 2, 5, 1]), enforce_sorted=False) if packed else xi
+            out, (hn, cn) = net(inp, (h0, c0))
+            data = out.data if packed else out
+            (data.square().sum() + hn.sum() + (0 if packed else cn.sum())).backward()
+            results.append((data, hn, cn, xi.grad, [p.grad.clone() for p in net.parameters()]))
+            net.zero_grad()
+        (o1, h1, c1, g1, p1), (o2, h2, c2, g2, p2) = results
+        assert o2.shape[-1] == P * nd and h2.shape == (L * nd, 4, P) and c2.shape == (L * nd, 4, H)
+        for a, b in ((o1, o2), (h1, h2), (c1, c2), (g1, g2)):
+            torch.testing.assert_close(a, b, rtol=1e-9, atol=1e-10)
+        for a, b in zip(p1, p2):
+            torch.testing.assert_close(a, b, rtol=1e-9, atol=1e-10)
+    # without initial states, and the constructor's checks
+    out, (hn, cn) = m(x)
+    ro, (rh, rc) = ref(x)
+    torch.testing.assert_close(out, ro, rtol=1e-9, atol=1e-10)
+    with pytest.raises(ValueError):
+        mod.FastLSTM(I, H, proj_size=H)
+    with pytest.raises(ValueError):
+        mod.FastLSTM(I, H, proj_size=-1)
