@@ -96,7 +96,8 @@ def test_forward_recurrence(dtype, shape):
 
 BWD_SHAPES = [(3, 128, 64), (5, 200, 128), (8, 256, 256), (4, 64, 1024), (6, 1300, 512), (1, 40, 64), (30, 96, 256),
               (3, 32, 2048), (4, 130, 1536), (4, 384, 1024), (5, 640, 1024), (3, 1280, 1024), (5, 130, 768),
-              (4, 2304, 256), (5, 1024, 512), (4, 640, 512), (3, 4800, 64), (3, 400, 768), (3, 2000, 320)]
+              (4, 2304, 256), (5, 1024, 512), (4, 640, 512), (3, 4800, 64), (3, 400, 768), (3, 2000, 320),
+              (5, 2560, 512), (3, 4096, 512)]
 
 
 def _bwd(lib, d, dout, dh_n, dc_n, ifgo, cell, Wh):
