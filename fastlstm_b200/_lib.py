@@ -19,6 +19,7 @@ FLAG_FORCE_GENERIC = 1
 FLAG_INFERENCE = 8
 FLAG_NO_FUSED = 32        # blstm_fwd: keep tiny sizes on projection + recurrence
 FLAG_NO_CLUSTER = 16      # forward: keep small hidden sizes on the general kernel
+FLAG_HALF_DEVICE = 128    # recurrences: plan for half of the SMs (two persistent kernels side by side)
 FLAG_TEST_NO_ARRIVE = 4   # test hook: no CTA signals step completion (every wait runs out)
 
 OK = 0

@@ -91,8 +91,9 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   // Wider slices when they fill the GPU AND leave every CTA two or more tiles to interleave (a single
   // tile of 32 units per CTA is latency bound and measured slower than two interleaved tiles of 16:
   // 2.12 against 1.87 ms at B=1024, H=512, T=256).
+  const int sm_share = (d.flags & BLSTM_FLAG_HALF_DEVICE) ? 2 : 1;   // half the device: two kernels side by side
   if (H <= 512 && p.nbt * (H / 32) >= 74) {
-    const int sms32 = plan_sm_count();
+    const int sms32 = plan_sm_count() / sm_share;
     int par32 = sms32 / (H / 32);
     if (par32 > p.nbt) par32 = p.nbt;
     if (par32 > 0 && cdiv(p.nbt, par32) >= 2) UH = 32;
@@ -100,7 +101,7 @@ static RecPlan make_plan(const blstm_desc& d, int phase) {
   p.UH = UH;
   p.N = 4 * UH;
   p.nh = H / UH;
-  const int sms = plan_sm_count();
+  const int sms = plan_sm_count() / sm_share;
   if (p.nh > sms) return p;
   p.nb_par = sms / p.nh;
   if (p.nb_par > p.nbt) p.nb_par = p.nbt;
@@ -851,7 +852,7 @@ static BwdPlan make_bwd_plan(const blstm_desc& d) {
   p.nbt = cdiv(B, RB);
   p.nug = H / 64;
   const int per_tile = p.nug * 4;
-  const int sms = std::min(plan_sm_count(), bwd_cta_capacity());
+  const int sms = std::min(plan_sm_count(), bwd_cta_capacity()) / ((d.flags & BLSTM_FLAG_HALF_DEVICE) ? 2 : 1);
   if (per_tile > sms) return p;
   p.nb_par = sms / per_tile;
   if (p.nb_par > p.nbt) p.nb_par = p.nbt;

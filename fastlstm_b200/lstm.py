@@ -147,12 +147,13 @@ def plan_detail(dtype, T, B, I, H, phase="fwd"):
 # ---------------------------------------------------------------------------
 # Operator functions (same names and argument meaning as the reference)
 # ---------------------------------------------------------------------------
-def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh, inference=False):
+def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh, inference=False, half_device=False):
     """Forward of one layer.  x [T,B,I]; h0,c0 [B,H] or None; Wx [4H,I]; Wh [4H,H];
     bx,bh [4H] or None.  Returns (out[T+1,B,H], cell[T+1,B,H], ifgo[T,B,4H]);
     slot 0 of out/cell is the initial state.  (fastlstm/lstm.py:31-146)
     inference=True: nothing is saved for backward - ifgo and cell[1..T-1] are left unwritten
-    (cell[T] is still c_n), which halves the bytes each step moves."""
+    (cell[T] is still c_n), which halves the bytes each step moves.
+    half_device=True: the recurrence is planned for half of the SMs (two layers side by side)."""
     lib = _lib.load()
     if x.dim() == 2:
         x = x[None]
@@ -168,7 +169,7 @@ def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh, inference=False):
         raise ValueError("h0 and c0 must both be given or both be None")
     _require(h0, "h0", dt, (B, H), dev)
     _require(c0, "c0", dt, (B, H), dev)
-    d = _desc(dt, T, B, I, H, _lib.FLAG_INFERENCE if inference else 0)
+    d = _desc(dt, T, B, I, H, (_lib.FLAG_INFERENCE if inference else 0) | (_lib.FLAG_HALF_DEVICE if half_device else 0))
     with torch.cuda.device(dev):
         states = torch.empty((2, T + 1, B, H), device=dev, dtype=dt)
         out, cell = states.unbind(0)
@@ -182,7 +183,7 @@ def lstm_persistent_fwd(x, h0, c0, Wx, bx, Wh, bh, inference=False):
     return out, cell, ifgo
 
 
-def lstm_persistent_bwd(dh, dc_n, dh_n, x, h, cell, ifgo, Wx, Wh, need_dx=True, wgrads=None):
+def lstm_persistent_bwd(dh, dc_n, dh_n, x, h, cell, ifgo, Wx, Wh, need_dx=True, wgrads=None, half_device=False):
     """Backward of one layer.  dh [T,B,H] gradient of out[1:]; dc_n, dh_n [B,H]
     (or None) gradients of the final states; h = out[T+1,B,H] from forward.
     Returns (d_x, dh_0, dc_0, dWx, dbx, dWh, dbh); weight and bias gradients are
@@ -200,7 +201,7 @@ def lstm_persistent_bwd(dh, dc_n, dh_n, x, h, cell, ifgo, Wx, Wh, need_dx=True, 
     _require(h, "h", dt, (T + 1, B, H), dev)
     _require(cell, "cell", dt, (T + 1, B, H), dev)
     _require(ifgo, "ifgo", dt, (T, B, 4 * H), dev)
-    d = _desc(dt, T, B, I, H)
+    d = _desc(dt, T, B, I, H, _lib.FLAG_HALF_DEVICE if half_device else 0)
     with torch.cuda.device(dev):
         d_ifgo = torch.empty_like(ifgo)
         d_x = torch.empty((T, B, I), device=dev, dtype=dt) if need_dx else None
@@ -380,6 +381,162 @@ class PersistentLSTMfn(torch.autograd.Function):
                 dbh if ctx.has_bias[1] else None, None, None, None)
 
 
+_side_streams = {}
+
+
+def _side_stream(device):
+    """One extra stream per device for the layer wavefront (created once, reused)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=key)
+    return _side_streams[key]
+
+
+class WavefrontLSTMfn(torch.autograd.Function):
+    """A unidirectional stack of layers as ONE autograd node that runs the layers as a wavefront over
+    time chunks: layer l works on chunk k while layer l-1 works on chunk k+1, on two streams, each
+    recurrence planned for half of the SMs (the reference runs the layers one after the other,
+    fastlstm/lstm.py:685-696, and lists the wavefront as missing, README.md:94).  It pays when a
+    layer alone cannot fill the GPU: few batch tiles, every CTA with one tile, every step one
+    hand-off chain.  A chunk is an ordinary call of the layer operators with the previous chunk's
+    final state as its initial state (the cell state crosses a chunk boundary in the storage dtype).
+
+    forward(x[T,B,I], n_chunks, sinks, h0, c0, *params) with params = (Wx, bx, Wh, bh) per layer,
+    h0/c0 [L,B,H] or None  ->  (out[T,B,H], h_n[L,B,H], c_n[L,B,H])."""
+
+    @staticmethod
+    def forward(ctx, x, n_chunks, sinks, h0, c0, *params):
+        L = len(params) // 4
+        T = x.shape[0]
+        x = x.contiguous()
+        bounds = [(T * k) // n_chunks for k in range(n_chunks + 1)]
+        chunks = [(bounds[k], bounds[k + 1]) for k in range(n_chunks) if bounds[k + 1] > bounds[k]]
+        NC = len(chunks)
+        main = torch.cuda.current_stream(x.device)
+        streams = [main, _side_stream(x.device)]
+        streams[1].wait_stream(main)
+        saved = [[None] * NC for _ in range(L)]
+        done = [[None] * NC for _ in range(L)]
+        with torch.autograd.profiler.record_function("fastlstm_b200::wavefront_fwd"):
+            for diag in range(NC + L - 1):
+                for l in range(L):
+                    k = diag - l
+                    if k < 0 or k >= NC:
+                        continue
+                    Wx, bx, Wh, bh = params[4 * l:4 * l + 4]
+                    st = streams[l % 2]
+                    if l > 0:
+                        st.wait_event(done[l - 1][k])
+                    with torch.cuda.stream(st):
+                        t0, t1 = chunks[k]
+                        xc = x[t0:t1] if l == 0 else saved[l - 1][k][1][1:]
+                        if k == 0:
+                            hp = None if h0 is None else h0[l].contiguous()
+                            cp = None if c0 is None else c0[l].contiguous()
+                        else:
+                            hp, cp = saved[l][k - 1][1][-1], saved[l][k - 1][2][-1]
+                        out, cell, ifgo = lstm_persistent_fwd(xc, hp, cp, Wx.contiguous(), bx, Wh.contiguous(), bh,
+                                                              inference=False, half_device=True)
+                        saved[l][k] = (xc, out, cell, ifgo)
+                        done[l][k] = torch.cuda.Event()
+                        done[l][k].record(st)
+            # every later use (the concatenation below, backward, the allocator) comes after both streams
+            main.wait_stream(streams[1])
+            streams[1].wait_stream(main)
+            top = saved[L - 1]
+            y = torch.cat([top[k][1][1:] for k in range(NC)], dim=0) if NC > 1 else top[0][1][1:].clone()
+            h_n = torch.stack([saved[l][NC - 1][1][-1] for l in range(L)])
+            c_n = torch.stack([saved[l][NC - 1][2][-1] for l in range(L)])
+        ctx.saved = saved
+        ctx.params = params
+        ctx.sinks = sinks
+        ctx.chunks = chunks
+        ctx.had_state = h0 is not None
+        return y, h_n, c_n
+
+    @staticmethod
+    def backward(ctx, d_out, d_hn, d_cn):
+        saved, params, chunks, sinks = ctx.saved, ctx.params, ctx.chunks, ctx.sinks
+        L, NC = len(saved), len(chunks)
+        x0 = saved[0][0][0]
+        dt, dev = x0.dtype, x0.device
+        B, H = saved[0][0][1].shape[1], saved[0][0][1].shape[2]
+        main = torch.cuda.current_stream(dev)
+        streams = [main, _side_stream(dev)]
+        streams[1].wait_stream(main)
+        d_out = None if d_out is None else d_out.to(dt).contiguous()
+        d_hn = None if d_hn is None else d_hn.to(dt).contiguous()
+        d_cn = None if d_cn is None else d_cn.to(dt).contiguous()
+        need_dx0 = ctx.needs_input_grad[0]
+        dx = [[None] * NC for _ in range(L)]
+        carry = [[None] * NC for _ in range(L)]
+        done = [[None] * NC for _ in range(L)]
+        acc = [None] * L
+        with torch.autograd.profiler.record_function("fastlstm_b200::wavefront_bwd"):
+            for diag in range(NC + L - 1):
+                for li in range(L):
+                    l = L - 1 - li
+                    k = NC - 1 - (diag - li)
+                    if k < 0 or k >= NC:
+                        continue
+                    Wx, bx, Wh, bh = params[4 * l:4 * l + 4]
+                    st = streams[l % 2]
+                    if l < L - 1:
+                        st.wait_event(done[l + 1][k])
+                    with torch.cuda.stream(st):
+                        xc, out, cell, ifgo = saved[l][k]
+                        t0, t1 = chunks[k]
+                        if l == L - 1:
+                            dh = d_out[t0:t1] if d_out is not None else torch.zeros((t1 - t0, B, H), device=dev, dtype=dt)
+                        else:
+                            dh = dx[l + 1][k]
+                        if k == NC - 1:
+                            dh_n = None if d_hn is None else d_hn[l]
+                            dc_n = None if d_cn is None else d_cn[l]
+                        else:
+                            dh_n, dc_n = carry[l][k + 1]
+                        I = xc.shape[-1]
+                        first = acc[l] is None
+                        buf = torch.empty(4 * H * (I + H + 1), device=dev, dtype=torch.float32)
+                        d_x, dh_0, dc_0, _, _, _, _ = lstm_persistent_bwd(
+                            dh, dc_n, dh_n, xc, out, cell, ifgo, Wx.contiguous(), Wh.contiguous(),
+                            need_dx=(l > 0 or need_dx0), wgrads=buf, half_device=True)
+                        if first:
+                            acc[l] = buf
+                        else:
+                            acc[l].add_(buf)
+                        dx[l][k], carry[l][k] = d_x, (dh_0, dc_0)
+                        if k == 0 and sinks is not None:
+                            # the layer's fp32 gradients go straight into its bucket segment, whose
+                            # all-reduce starts here, beside the backward of the layers below
+                            sinks[l].buffer.copy_(acc[l])
+                            sinks[l].filled()
+                        done[l][k] = torch.cuda.Event()
+                        done[l][k].record(st)
+            main.wait_stream(streams[1])
+            streams[1].wait_stream(main)
+            d_x = None
+            if need_dx0:
+                d_x = torch.cat(dx[0], dim=0) if NC > 1 else dx[0][0]
+            dh0 = dc0 = None
+            if ctx.had_state:
+                dh0 = torch.stack([carry[l][0][0] for l in range(L)])
+                dc0 = torch.stack([carry[l][0][1] for l in range(L)])
+        grads = []
+        for l in range(L):
+            Wx, bx, Wh, bh = params[4 * l:4 * l + 4]
+            if sinks is not None:
+                grads += [None, None, None, None]
+                continue
+            I = Wx.shape[1]
+            dWx = acc[l][:4 * H * I].view(4 * H, I)
+            dWh = acc[l][4 * H * I:4 * H * (I + H)].view(4 * H, H)
+            db = acc[l][4 * H * (I + H):]
+            grads += [dWx, db if bx is not None else None, dWh, db if bh is not None else None]
+        ctx.saved = None
+        return (d_x, None, None, dh0, dc0, *grads)
+
+
 def _nothing_to_save(*tensors):
     """True when no backward can follow this forward: grad mode is off, or no input requires one."""
     return not (torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors))
@@ -504,8 +661,57 @@ class FastLSTM(nn.Module):
         data = pack_padded_sequence(out, lengths, enforce_sorted=True).data
         return PackedSequence(data, seq.batch_sizes, seq.sorted_indices, seq.unsorted_indices), states
 
+    def _wavefront_chunks(self, x, h_c_0, lengths):
+        """Number of time chunks for the layer wavefront, or 0 when the stack runs layer after layer.
+        The wavefront needs two or more layers of one direction on the tensor-core kernels and pays
+        when a layer alone leaves the GPU latency bound: every CTA has a single batch tile on the
+        whole device and at most two on half of it."""
+        if os.environ.get("FASTLSTM_B200_WAVEFRONT", "1") == "0":
+            return 0
+        if (self.num_layers < 2 or self.num_directions != 1 or self.proj_size > 0 or lengths is not None
+                or (self.dropout > 0.0 and self.training) or not x.is_cuda
+                or x.dtype not in (torch.float16, torch.bfloat16) or torch.is_autocast_enabled("cuda")):
+            return 0
+        T, B, I = x.shape
+        H = self.hidden_size
+        if H % 64 != 0 or H > 1024 or I % 8 != 0 or T < 64:
+            return 0
+        if any(p.dtype != x.dtype for p in self.parameters()):
+            return 0
+        if _nothing_to_save(x, *self.parameters()):
+            return 0
+        sms = 148
+        tiles, ctas_per_tile = -(-B // 128), H // 16
+        if tiles < 2 or ctas_per_tile > sms // 2:
+            return 0
+        if tiles > sms // ctas_per_tile or tiles > 2 * ((sms // 2) // ctas_per_tile):
+            return 0
+        return max(1, min(int(os.environ.get("FASTLSTM_B200_WAVEFRONT_CHUNKS", "4")), T // 16))
+
+    def _forward_wavefront(self, x, h_c_0, n_chunks):
+        h0 = c0 = None
+        if h_c_0 is not None:
+            h0, c0 = h_c_0
+            if h0 is None or c0 is None:
+                raise ValueError("h_c_0 must be a pair (h_0, c_0) of [num_layers, B, H] tensors or None")
+            h0 = torch.stack(list(h0)) if not torch.is_tensor(h0) else h0
+            c0 = torch.stack(list(c0)) if not torch.is_tensor(c0) else c0
+            if h0.shape[0] != self.num_layers or c0.shape[0] != self.num_layers:
+                raise ValueError(f"expected {self.num_layers} initial states, got {h0.shape[0]} / {c0.shape[0]}")
+            h0, c0 = h0.to(x.dtype), c0.to(x.dtype)
+        params = []
+        for layer in range(self.num_layers):
+            params += list(self.layer_params(layer))
+        out, h_n, c_n = WavefrontLSTMfn.apply(x, n_chunks, self._sinks, h0, c0, *params)
+        if self.batch_first:
+            out = out.transpose(0, 1)
+        return out, (h_n, c_n)
+
     def _forward_padded(self, x, h_c_0, lengths):
         """x [T,B,I]; lengths: None, or the [B] valid lengths (device tensor) of padded sequences."""
+        n_chunks = self._wavefront_chunks(x, h_c_0, lengths)
+        if n_chunks:
+            return self._forward_wavefront(x, h_c_0, n_chunks)
         nd = self.num_directions
         T, B = x.shape[0], x.shape[1]
         if lengths is not None:

@@ -60,6 +60,8 @@ enum {
   BLSTM_FLAG_NO_FUSED = 32,     /* blstm_fwd: do not use the single-kernel forward (projection inside the
                                    time loop) that tiny sizes (max(H, I) <= 32 in fp32, <= 64 in 16 bit)
                                    otherwise get; for comparisons and tests */
+  BLSTM_FLAG_HALF_DEVICE = 128, /* recurrences: plan for half of the SMs, so that two persistent kernels (two
+                                   layers of a stack working on neighbouring time chunks) fit side by side */
   BLSTM_FLAG_NO_CLUSTER = 16,   /* forward: do not use the cluster hand-off kernel that small hidden
                                    sizes (H = 64, 128, 256 with at most 7 batch tiles) otherwise get;
                                    for comparisons and tests */

@@ -190,3 +190,49 @@ def test_proj_size_matches_nn_lstm(dtype, bidirectional, H, P):
             assert np.abs(got[k] - want[k]).max() <= 2e-2, k
         else:
             assert max_rel(got[k], want[k]) <= 5e-2, k
+
+
+@pytest.mark.parametrize("B,states", [(512, False), (300, True)])
+def test_layer_wavefront_matches_the_sequential_stack(monkeypatch, B, states):
+    """Two layers, few batch tiles: the stack runs as a wavefront over time chunks on two streams
+    (layer 1 on chunk k beside layer 0 on chunk k+1).  Same results as the layers run one after the
+    other, up to the cell state crossing chunk boundaries in bf16; gradients of inputs, initial states
+    and parameters included."""
+    import fastlstm_b200 as F
+    T, I, H, L = 96, 512, 512, 2
+    dt = torch.bfloat16
+    torch.manual_seed(5)
+    m = F.FastLSTM(I, H, num_layers=L, device="cuda", dtype=dt)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(T, B, I, generator=g, device="cuda").to(dt)
+    dout = torch.randn(T, B, H, generator=g, device="cuda").to(dt)
+    dhn = torch.randn(L, B, H, generator=g, device="cuda").to(dt)
+    h0 = (torch.randn(L, B, H, generator=g, device="cuda") * 0.1).to(dt)
+    c0 = (torch.randn(L, B, H, generator=g, device="cuda") * 0.1).to(dt)
+    assert m._wavefront_chunks(x.requires_grad_(True), None, None) == 4
+
+    def run(on):
+        monkeypatch.setenv("FASTLSTM_B200_WAVEFRONT", "1" if on else "0")
+        xi = x.detach().clone().requires_grad_(True)
+        st = (h0.clone().requires_grad_(True), c0.clone().requires_grad_(True)) if states else None
+        m.zero_grad()
+        out, (hn, cn) = m(xi, st)
+        torch.autograd.backward([out, hn], [dout, dhn])
+        torch.cuda.synchronize()
+        F.check_status()
+        res = {"out": out, "h_n": hn, "c_n": cn, "dx": xi.grad}
+        if states:
+            res["dh0"], res["dc0"] = st[0].grad, st[1].grad
+        for n, p in m.named_parameters():
+            res["grad:" + n] = p.grad.clone()
+        return {k: v.detach().float().cpu().numpy() for k, v in res.items()}
+
+    want, got = run(False), run(True)
+    for k in want:
+        if k in ("out", "h_n", "c_n"):
+            assert np.abs(got[k] - want[k]).max() <= 2e-2, k
+        else:
+            assert max_rel(got[k], want[k]) <= 3e-2, k
+    again = run(True)
+    for k in got:
+        assert np.array_equal(got[k], again[k]), k      # deterministic
