@@ -405,7 +405,11 @@ def main():
     # launching stream); the slower one is the dominant kernel of the step and goes in "roofline"
     hbm_gbs, tflops, which = peaks()
     es = ESIZE[cfg["dtype"]]
-    d = _lib.Desc(_lib.DTYPE_CODE[cfg["dtype"]], T, B, H, H, 0 if cfg["bwd"] else _lib.FLAG_INFERENCE, 0, 0)
+    # small shards of a stack run as a layer wavefront (two layers side by side, each recurrence planned
+    # for half of the SMs): the kernels are then timed, and their plans reported, as the step runs them
+    wave = model._wavefront_chunks(x_dev, None, None) if hasattr(model, "_wavefront_chunks") else 0
+    kflags = (0 if cfg["bwd"] else _lib.FLAG_INFERENCE) | (_lib.FLAG_HALF_DEVICE if wave else 0)
+    d = _lib.Desc(_lib.DTYPE_CODE[cfg["dtype"]], T, B, H, H, kflags, 0, 0)
     st = torch.cuda.current_stream().cuda_stream
     Wh = model.weight_hh_l0.detach()
     pre = (torch.randn(T, B, 4 * H, device=dev) * 0.5).to(dt)
@@ -459,6 +463,12 @@ def main():
     hbm_time = alg_bytes / (hbm_gbs * 1e9)
     tensor_time = alg_flops / (tflops * 1e12)
 
+    def plan_text(phase):
+        import ctypes
+        buf = ctypes.create_string_buffer(512)
+        lib.blstm_plan_detail(d, phase, buf, 512)
+        return buf.value.decode()
+
     def roof_of(name, ms):
         if hbm_time >= tensor_time:
             r = {"bound": "hbm", "achieved": alg_bytes / (ms * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s"}
@@ -491,7 +501,9 @@ def main():
         "dtype": cfg["dtype"], "data": "synthetic",
         "config": workload_config(wl, cfg, world, args.seq_len > 0, args.batch > 0),
         "collective": "fp32 sum-allreduce of dWx,dWh,db, one per layer, started from that layer's backward (NCCL)" if bucket is not None else "none",
-        "plans": {"fwd": F.plan_detail(dt, T, B, H, H, "fwd"), "bwd": F.plan_detail(dt, T, B, H, H, "bwd")},
+        "plans": {"fwd": plan_text(0), "bwd": plan_text(1)},
+        "layer_wavefront": ("%d time chunks, two layers side by side on two streams, each recurrence on half of the SMs" % wave)
+                           if wave else "off (layers run one after the other)",
         "us_per_timestep": ms_step * 1e3 / (T * L),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": x_host.numel() * es * world,
