@@ -533,7 +533,6 @@ class WavefrontLSTMfn(torch.autograd.Function):
             dWh = acc[l][4 * H * I:4 * H * (I + H)].view(4 * H, H)
             db = acc[l][4 * H * (I + H):]
             grads += [dWx, db if bx is not None else None, dWh, db if bh is not None else None]
-        ctx.saved = None
         return (d_x, None, None, dh0, dc0, *grads)
 
 
