@@ -401,11 +401,12 @@ class WavefrontLSTMfn(torch.autograd.Function):
     hand-off chain.  A chunk is an ordinary call of the layer operators with the previous chunk's
     final state as its initial state (the cell state crosses a chunk boundary in the storage dtype).
 
-    forward(x[T,B,I], n_chunks, sinks, h0, c0, *params) with params = (Wx, bx, Wh, bh) per layer,
-    h0/c0 [L,B,H] or None  ->  (out[T,B,H], h_n[L,B,H], c_n[L,B,H])."""
+    forward(x[T,B,I], n_chunks, sinks, inference, h0, c0, *params) with params = (Wx, bx, Wh, bh) per
+    layer, h0/c0 [L,B,H] or None  ->  (out[T,B,H], h_n[L,B,H], c_n[L,B,H]).  inference=True: nothing is
+    saved for backward and the recurrences skip the stores only backward needs."""
 
     @staticmethod
-    def forward(ctx, x, n_chunks, sinks, h0, c0, *params):
+    def forward(ctx, x, n_chunks, sinks, inference, h0, c0, *params):
         L = len(params) // 4
         T = x.shape[0]
         x = x.contiguous()
@@ -436,8 +437,8 @@ class WavefrontLSTMfn(torch.autograd.Function):
                         else:
                             hp, cp = saved[l][k - 1][1][-1], saved[l][k - 1][2][-1]
                         out, cell, ifgo = lstm_persistent_fwd(xc, hp, cp, Wx.contiguous(), bx, Wh.contiguous(), bh,
-                                                              inference=False, half_device=True)
-                        saved[l][k] = (xc, out, cell, ifgo)
+                                                              inference=bool(inference), half_device=True)
+                        saved[l][k] = (xc, out, cell, None if inference else ifgo)
                         done[l][k] = torch.cuda.Event()
                         done[l][k].record(st)
             # every later use (the concatenation below, backward, the allocator) comes after both streams
@@ -447,15 +448,19 @@ class WavefrontLSTMfn(torch.autograd.Function):
             y = torch.cat([top[k][1][1:] for k in range(NC)], dim=0) if NC > 1 else top[0][1][1:].clone()
             h_n = torch.stack([saved[l][NC - 1][1][-1] for l in range(L)])
             c_n = torch.stack([saved[l][NC - 1][2][-1] for l in range(L)])
-        ctx.saved = saved
-        ctx.params = params
-        ctx.sinks = sinks
-        ctx.chunks = chunks
-        ctx.had_state = h0 is not None
+        ctx.inference = bool(inference)
+        if not inference:
+            ctx.saved = saved
+            ctx.params = params
+            ctx.sinks = sinks
+            ctx.chunks = chunks
+            ctx.had_state = h0 is not None
         return y, h_n, c_n
 
     @staticmethod
     def backward(ctx, d_out, d_hn, d_cn):
+        if ctx.inference:
+            raise RuntimeError("this forward ran in inference mode (nothing was saved); backward is not possible")
         saved, params, chunks, sinks = ctx.saved, ctx.params, ctx.chunks, ctx.sinks
         L, NC = len(saved), len(chunks)
         x0 = saved[0][0][0]
@@ -533,7 +538,7 @@ class WavefrontLSTMfn(torch.autograd.Function):
             dWh = acc[l][4 * H * I:4 * H * (I + H)].view(4 * H, H)
             db = acc[l][4 * H * (I + H):]
             grads += [dWx, db if bx is not None else None, dWh, db if bh is not None else None]
-        return (d_x, None, None, dh0, dc0, *grads)
+        return (d_x, None, None, None, dh0, dc0, *grads)
 
 
 def _nothing_to_save(*tensors):
@@ -677,8 +682,6 @@ class FastLSTM(nn.Module):
             return 0
         if any(p.dtype != x.dtype for p in self.parameters()):
             return 0
-        if _nothing_to_save(x, *self.parameters()):
-            return 0
         sms = 148
         tiles, ctas_per_tile = -(-B // 128), H // 16
         if tiles < 2 or ctas_per_tile > sms // 2:
@@ -701,7 +704,8 @@ class FastLSTM(nn.Module):
         params = []
         for layer in range(self.num_layers):
             params += list(self.layer_params(layer))
-        out, h_n, c_n = WavefrontLSTMfn.apply(x, n_chunks, self._sinks, h0, c0, *params)
+        inference = _nothing_to_save(x, h0, c0, *params)
+        out, h_n, c_n = WavefrontLSTMfn.apply(x, n_chunks, self._sinks, inference, h0, c0, *params)
         if self.batch_first:
             out = out.transpose(0, 1)
         return out, (h_n, c_n)

@@ -236,3 +236,10 @@ def test_layer_wavefront_matches_the_sequential_stack(monkeypatch, B, states):
     again = run(True)
     for k in got:
         assert np.array_equal(got[k], again[k]), k      # deterministic
+    # the same wavefront without anything saved for backward (inference): identical outputs
+    monkeypatch.setenv("FASTLSTM_B200_WAVEFRONT", "1")
+    with torch.no_grad():
+        out, (hn, cn) = m(x.detach(), (h0, c0) if states else None)
+    torch.cuda.synchronize()
+    F.check_status()
+    assert np.array_equal(out.float().cpu().numpy(), got["out"]) and np.array_equal(cn.float().cpu().numpy(), got["c_n"])
