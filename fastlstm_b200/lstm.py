@@ -684,7 +684,7 @@ class FastLSTM(nn.Module):
             return 0
         sms = 148
         tiles, ctas_per_tile = -(-B // 128), H // 16
-        if tiles < 2 or ctas_per_tile > sms // 2:
+        if ctas_per_tile > sms // 2:          # (a single tile's CTAs must fit on half of the SMs)
             return 0
         if tiles > sms // ctas_per_tile or tiles > 2 * ((sms // 2) // ctas_per_tile):
             return 0

@@ -192,7 +192,7 @@ def test_proj_size_matches_nn_lstm(dtype, bidirectional, H, P):
             assert max_rel(got[k], want[k]) <= 5e-2, k
 
 
-@pytest.mark.parametrize("B,states", [(512, False), (300, True)])
+@pytest.mark.parametrize("B,states", [(512, False), (300, True), (64, True)])
 def test_layer_wavefront_matches_the_sequential_stack(monkeypatch, B, states):
     """Two layers, few batch tiles: the stack runs as a wavefront over time chunks on two streams
     (layer 1 on chunk k beside layer 0 on chunk k+1).  Same results as the layers run one after the
